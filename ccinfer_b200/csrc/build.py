@@ -33,6 +33,7 @@ GROUPS = {
         "elementwise.cu",
         "norm.cu",
         "rope_kv.cu",
+        "delta_rule.cu",
         "attention_generic.cu",
         "attention_split.cu",
         "attention_decode_mma.cu",

@@ -1,0 +1,355 @@
+// Gated delta rule with one decay per head and key channel, as a recurrence over a state per request.
+//
+// Per head, with S a matrix [key channels, value channels] that starts at zero:
+//   S <- diag(g_t) S;  u_t = beta_t (v_t - S^T k_t);  S <- S + k_t u_t^T;  o_t = S^T q_t
+// q and k come through a short causal convolution per channel and silu, then are made unit vectors
+// per head (q also times dim^-1/2); v comes through its convolution and silu; beta = sigmoid(.),
+// g = exp(-exp(A_h) softplus(a + dt_bias)).  Everything after the projections is float.
+//
+// Four kernels:
+//   delta_prepare       one block per token: convolution + silu, unit norms, beta, decay -> float rows
+//   conv_state_update   the last (taps - 1) projection rows of each request -> its convolution state
+//   delta_recurrence    one block per (request, head, 32 value channels): walks the step's tokens of the
+//                       request in order; a column of S is independent of the others, so each is held by
+//                       8 lanes (rows r = 8 i + lane) in registers and two 8-lane sums per token give
+//                       S^T k and S^T q.  The rows of q, k, g of the next 16 tokens are fetched with
+//                       cp.async while the current ones are used.
+//   gated_head_rmsnorm  o / rms(o) * w * sigmoid(gate) per head -> the compute type
+//
+// State of a request (slot s): S as [heads, value channels, key channels] floats (a column of S is
+// contiguous), and the convolution's last (taps - 1) inputs as [taps - 1, channels] in the compute type.
+// Rows whose request has no slot (padding of a replayed step) are skipped.
+#include "common.cuh"
+
+using namespace ccb;
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// ---------------------------------------------------------------------------------------------
+// proj [T, ld]: columns q (at oq, G*dk), k (at ok, G*dk), v (at ov, H*dv), b (at ob, H); a [T, lda]: H*dk
+// decay pre-activations.  conv_w float [C, taps] for the channels q|k|v in this order (C = 2 G dk + H dv);
+// conv_state [slots, taps-1, C].
+template <typename T>
+__global__ void __launch_bounds__(256)
+delta_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov, int ob, const T* __restrict__ a,
+                     int lda, const float* __restrict__ conv_w, int taps, const T* __restrict__ conv_state,
+                     const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                     const int* __restrict__ entry_of_token, const int* __restrict__ cu_q,
+                     const int* __restrict__ state_slot, float* __restrict__ qn, float* __restrict__ kn,
+                     float* __restrict__ vv, float* __restrict__ gg, float* __restrict__ bb, int G, int H, int dk,
+                     int dv, float q_mult, float unit_eps) {
+  ccb::pdl_begin();
+  const int t = blockIdx.x;
+  const int e = entry_of_token[t];
+  if (e < 0) return;
+  const int slot = state_slot[e];
+  if (slot < 0) return;
+  const int lt = t - cu_q[e];  // index of the token within the step's portion of its request
+  const int C = 2 * G * dk + H * dv;
+  const T* st = conv_state + (size_t)slot * (taps - 1) * C;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+
+  // convolution + silu of channel c (in the order q | k | v), input column `col` of proj
+  auto conv = [&](int c, int col) -> float {
+    const float* w = conv_w + (size_t)c * taps;
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {  // tap j multiplies the input (taps - 1 - j) tokens back
+      const int back = taps - 1 - j;
+      const int li = lt - back;
+      float x;
+      if (li >= 0) x = to_f32(proj[(size_t)(t - back) * ld + col]);
+      else x = to_f32(st[(size_t)(taps - 1 + li) * C + c]);
+      acc += w[j] * x;
+    }
+    return acc * sigmoid_f(acc);
+  };
+
+  // units: G query heads, G key heads (unit vectors), H value heads, H decay rows
+  const int units = 2 * G + 2 * H;
+  for (int u = warp; u < units; u += n_warps) {
+    if (u < 2 * G) {
+      const bool is_q = u < G;
+      const int head = is_q ? u : u - G;
+      const int c0 = (is_q ? 0 : G * dk) + head * dk;
+      const int col0 = (is_q ? oq : ok) + head * dk;
+      float* dst = (is_q ? qn : kn) + ((size_t)t * G + head) * dk;
+      float ss = 0.f;
+      for (int i = lane; i < dk; i += 32) {
+        const float y = conv(c0 + i, col0 + i);
+        dst[i] = y;
+        ss += y * y;
+      }
+      ss = warp_sum(ss);
+      const float inv = (is_q ? q_mult : 1.0f) / sqrtf(ss + unit_eps);
+      for (int i = lane; i < dk; i += 32) dst[i] *= inv;  // each lane rescales what it wrote itself
+    } else if (u < 2 * G + H) {
+      const int head = u - 2 * G;
+      const int c0 = 2 * G * dk + head * dv;
+      float* dst = vv + ((size_t)t * H + head) * dv;
+      for (int i = lane; i < dv; i += 32) dst[i] = conv(c0 + i, ov + head * dv + i);
+      if (lane == 0) bb[(size_t)t * H + head] = sigmoid_f(to_f32(proj[(size_t)t * ld + ob + head]));
+    } else {
+      const int head = u - 2 * G - H;
+      const float rate = expf(A_log[head]);
+      float* dst = gg + ((size_t)t * H + head) * dk;
+      for (int i = lane; i < dk; i += 32) {
+        const float x = to_f32(a[(size_t)t * lda + head * dk + i]) + dt_bias[head * dk + i];
+        dst[i] = expf(-rate * softplus_f(x));
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov,
+                                         T* __restrict__ conv_state, int taps, const int* __restrict__ cu_q,
+                                         const int* __restrict__ state_slot, int G, int H, int dk, int dv) {
+  ccb::pdl_begin();
+  const int e = blockIdx.y;
+  const int slot = state_slot[e];
+  if (slot < 0) return;
+  const int C = 2 * G * dk + H * dv;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int col = c < G * dk ? oq + c : (c < 2 * G * dk ? ok + (c - G * dk) : ov + (c - 2 * G * dk));
+  const int r0 = cu_q[e], n = cu_q[e + 1] - r0;
+  if (n <= 0) return;
+  T* st = conv_state + (size_t)slot * (taps - 1) * C;
+  // new[i] is the input (taps - 1 - i) tokens before the end; in ascending i an old value is read before
+  // its place is written (it sits n >= 1 places further on)
+  for (int i = 0; i < taps - 1; ++i) {
+    const int li = n - (taps - 1) + i;
+    st[(size_t)i * C + c] = li >= 0 ? proj[(size_t)(r0 + li) * ld + col] : st[(size_t)(i + n) * C + c];
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+constexpr int kLanes = 8;          // lanes that share a column of S
+constexpr int kCols = 32;          // columns of S per block
+constexpr int kRecThreads = kLanes * kCols;
+
+__device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
+  const uint32_t s = (uint32_t)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(s), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
+// R: rows of S per lane (key channels padded to 8 R).  TCH tokens are staged at a time.
+template <int R>
+__global__ void __launch_bounds__(kRecThreads)
+delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
+                        const float* __restrict__ gg, const float* __restrict__ bb, float* __restrict__ state,
+                        float* __restrict__ out, const int* __restrict__ cu_q, const int* __restrict__ state_slot,
+                        int G, int H, int dk, int dv, int tch) {
+  ccb::pdl_begin();
+  constexpr int DP = R * kLanes;
+  extern __shared__ float smem[];
+  const int e = blockIdx.z, head = blockIdx.y;
+  const int slot = state_slot[e];
+  if (slot < 0) return;
+  const int r0 = cu_q[e], n = cu_q[e + 1] - r0;
+  if (n <= 0) return;
+  const int kvh = head / (H / G);
+  const int lane = threadIdx.x & (kLanes - 1);
+  const int cl = threadIdx.x / kLanes;
+  const int col = blockIdx.x * kCols + cl;
+  const bool live = col < dv;
+  // a stage: q, k, g rows [tch][DP] each, then v [tch][kCols], then beta [tch]
+  const int stage_floats = tch * (3 * DP + kCols + 1);
+  auto sq = [&](int s) { return smem + (size_t)s * stage_floats; };
+
+  // rows past dk never change: q = k = 0, g = 1 there (the loads never touch them)
+  for (int s = 0; s < 2; ++s) {
+    float* base = sq(s);
+    for (int i = threadIdx.x; i < tch * DP; i += kRecThreads) {
+      if (i % DP >= dk) {
+        base[i] = 0.f;
+        base[tch * DP + i] = 0.f;
+        base[2 * tch * DP + i] = 1.f;
+      }
+    }
+  }
+
+  auto fetch = [&](int chunk, int s) {
+    float* base = sq(s);
+    const int t0 = chunk * tch;
+    const int cnt = min(tch, n - t0);
+    for (int i = threadIdx.x; i < cnt * dk; i += kRecThreads) {
+      const int tt = i / dk, r = i - tt * dk;
+      const size_t row = (size_t)(r0 + t0 + tt);
+      cp_async4(base + tt * DP + r, qn + (row * G + kvh) * dk + r);
+      cp_async4(base + tch * DP + tt * DP + r, kn + (row * G + kvh) * dk + r);
+      cp_async4(base + 2 * tch * DP + tt * DP + r, gg + (row * H + head) * dk + r);
+    }
+    float* sv = base + 3 * tch * DP;
+    for (int i = threadIdx.x; i < cnt * kCols; i += kRecThreads) {
+      const int tt = i / kCols, c = i - tt * kCols;
+      const int gc = blockIdx.x * kCols + c;
+      if (gc < dv) cp_async4(sv + i, vv + ((size_t)(r0 + t0 + tt) * H + head) * dv + gc);
+    }
+    float* sb = sv + tch * kCols;
+    for (int i = threadIdx.x; i < cnt; i += kRecThreads) cp_async4(sb + i, bb + (size_t)(r0 + t0 + i) * H + head);
+    cp_async_commit();
+  };
+
+  float S[R];
+  float* sp = state + (((size_t)slot * H + head) * dv + (live ? col : 0)) * dk;
+#pragma unroll
+  for (int i = 0; i < R; ++i) {
+    const int r = i * kLanes + lane;
+    S[i] = (live && r < dk) ? sp[r] : 0.f;
+  }
+
+  const int chunks = (n + tch - 1) / tch;
+  fetch(0, 0);
+  for (int c = 0; c < chunks; ++c) {
+    cp_async_wait_all();
+    __syncthreads();  // chunk c is in stage c & 1; everyone is done with stage (c + 1) & 1
+    if (c + 1 < chunks) fetch(c + 1, (c + 1) & 1);
+    const float* base = sq(c & 1);
+    const float* sv = base + 3 * tch * DP;
+    const float* sb = sv + tch * kCols;
+    const int cnt = min(tch, n - c * tch);
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float* q = base + tt * DP;
+      const float* k = base + tch * DP + tt * DP;
+      const float* g = base + 2 * tch * DP + tt * DP;
+      float kr[R];
+      float dot = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        kr[i] = k[i * kLanes + lane];
+        S[i] *= g[i * kLanes + lane];
+        dot = fmaf(S[i], kr[i], dot);
+      }
+#pragma unroll
+      for (int o = kLanes / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = sb[tt] * (sv[tt * kCols + cl] - dot);
+      float od = 0.f;
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        S[i] = fmaf(kr[i], u, S[i]);
+        od = fmaf(S[i], q[i * kLanes + lane], od);
+      }
+#pragma unroll
+      for (int o = kLanes / 2; o > 0; o >>= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
+      if (live && lane == 0) out[((size_t)(r0 + c * tch + tt) * H + head) * dv + col] = od;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int r = i * kLanes + lane;
+      if (r < dk) sp[r] = S[i];
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * sigmoid(gate[t, h, :]); one warp per (t, h)
+template <typename T>
+__global__ void gated_head_rmsnorm_kernel(T* __restrict__ y, const float* __restrict__ o, const T* __restrict__ gate,
+                                          int ldg, const float* __restrict__ w, int rows, int H, int dv, float eps) {
+  ccb::pdl_begin();
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= rows * H) return;
+  const int lane = threadIdx.x & 31;
+  const int t = unit / H, h = unit - t * H;
+  const float* src = o + (size_t)unit * dv;
+  float ss = 0.f;
+  for (int i = lane; i < dv; i += 32) ss += src[i] * src[i];
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  const T* gr = gate + (size_t)t * ldg + (size_t)h * dv;
+  T* dst = y + (size_t)unit * dv;
+  for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(src[i] * inv * w[i] * sigmoid_f(to_f32(gr[i])));
+}
+
+}  // namespace
+
+CCB_API int ccb_delta_prepare(const void* proj, int ld, int oq, int ok, int ov, int ob, const void* a, int lda,
+                              const float* conv_w, int taps, const void* conv_state, const float* A_log,
+                              const float* dt_bias, const int* entry_of_token, const int* cu_q,
+                              const int* state_slot, float* qn, float* kn, float* vv, float* gg, float* bb, int T_,
+                              int G, int H, int dk, int dv, float q_mult, float unit_eps, int dtype,
+                              cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (G <= 0 || H <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 1) return CCB_REFUSE_SIZE;
+  if (dtype == CCB_F32)
+    ccb_launch(delta_prepare_kernel<float>, dim3(T_), dim3(256), 0, stream, (const float*)proj, ld, oq, ok, ov, ob,
+               (const float*)a, lda, conv_w, taps, (const float*)conv_state, A_log, dt_bias, entry_of_token, cu_q,
+               state_slot, qn, kn, vv, gg, bb, G, H, dk, dv, q_mult, unit_eps);
+  else if (dtype == CCB_BF16)
+    ccb_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(T_), dim3(256), 0, stream, (const __nv_bfloat16*)proj, ld,
+               oq, ok, ov, ob, (const __nv_bfloat16*)a, lda, conv_w, taps, (const __nv_bfloat16*)conv_state, A_log,
+               dt_bias, entry_of_token, cu_q, state_slot, qn, kn, vv, gg, bb, G, H, dk, dv, q_mult, unit_eps);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
+CCB_API int ccb_conv_state_update(const void* proj, int ld, int oq, int ok, int ov, void* conv_state, int taps,
+                                  const int* cu_q, const int* state_slot, int n_entries, int G, int H, int dk,
+                                  int dv, int dtype, cudaStream_t stream) {
+  if (n_entries <= 0 || taps <= 1) return 0;
+  const int C = 2 * G * dk + H * dv;
+  dim3 grid((C + 255) / 256, n_entries);
+  if (dtype == CCB_F32)
+    ccb_launch(conv_state_update_kernel<float>, grid, dim3(256), 0, stream, (const float*)proj, ld, oq, ok, ov,
+               (float*)conv_state, taps, cu_q, state_slot, G, H, dk, dv);
+  else if (dtype == CCB_BF16)
+    ccb_launch(conv_state_update_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (const __nv_bfloat16*)proj, ld,
+               oq, ok, ov, (__nv_bfloat16*)conv_state, taps, cu_q, state_slot, G, H, dk, dv);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
+CCB_API int ccb_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* gg,
+                                 const float* bb, float* state, float* out, const int* cu_q, const int* state_slot,
+                                 int n_entries, int G, int H, int dk, int dv, cudaStream_t stream) {
+  if (n_entries <= 0) return 0;
+  if (G <= 0 || H <= 0 || H % G || dk <= 0 || dk > 256 || dv <= 0) return CCB_REFUSE_SIZE;
+  int R = 1;
+  while (R * kLanes < dk) R *= 2;
+  const int DP = R * kLanes;
+  const int tch = DP <= 128 ? 16 : 8;
+  const size_t smem = (size_t)2 * tch * (3 * DP + kCols + 1) * sizeof(float);
+  dim3 grid((dv + kCols - 1) / kCols, H, n_entries);
+#define CCB_REC(RR)                                                                                              \
+  cudaFuncSetAttribute(delta_recurrence_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+  ccb_launch(delta_recurrence_kernel<RR>, grid, dim3(kRecThreads), smem, stream, qn, kn, vv, gg, bb, state, out, \
+             cu_q, state_slot, G, H, dk, dv, tch)
+  switch (R) {
+    case 1: CCB_REC(1); break;
+    case 2: CCB_REC(2); break;
+    case 4: CCB_REC(4); break;
+    case 8: CCB_REC(8); break;
+    case 16: CCB_REC(16); break;
+    default: CCB_REC(32); break;
+  }
+#undef CCB_REC
+  return ccb_launch_status();
+}
+
+CCB_API int ccb_gated_head_rmsnorm(void* y, const float* o, const void* gate, int ldg, const float* w, int rows,
+                                   int H, int dv, float eps, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (H <= 0 || dv <= 0) return CCB_REFUSE_SIZE;
+  const int units = rows * H;
+  dim3 grid((units + 7) / 8);
+  if (dtype == CCB_F32)
+    ccb_launch(gated_head_rmsnorm_kernel<float>, grid, dim3(256), 0, stream, (float*)y, o, (const float*)gate, ldg, w,
+               rows, H, dv, eps);
+  else if (dtype == CCB_BF16)
+    ccb_launch(gated_head_rmsnorm_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)y, o,
+               (const __nv_bfloat16*)gate, ldg, w, rows, H, dv, eps);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}

@@ -147,3 +147,42 @@ CCB_API int ccb_silu_mul(void* act, const void* gate_up, int T_, int F, int bloc
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
 }
+
+// Gated activation with clamped inputs:
+//   g = min(gate, limit), u = clamp(up, -limit, limit);  act = g * sigmoid(alpha * g) * (u + up_shift)
+// over the same two layouts of the merged gate|up columns as silu_mul.  Arithmetic in float.
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ act, const T* __restrict__ gu, int F, int B, size_t total,
+                                   float limit, float alpha, float up_shift) {
+  ccb::pdl_begin();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    const size_t t = i / F;
+    const int f = (int)(i - t * F);
+    const T* row = gu + t * 2 * (size_t)F;
+    const int gi = (f / B) * 2 * B + f % B;
+    const float g = fminf(to_f32(row[gi]), limit);
+    const float u = fminf(fmaxf(to_f32(row[gi + B]), -limit), limit);
+    act[i] = from_f32<T>(g / (1.0f + expf(-alpha * g)) * (u + up_shift));
+  }
+}
+
+CCB_API int ccb_clamped_glu(void* act, const void* gate_up, int T_, int F, int block, float limit, float alpha,
+                            float up_shift, int dtype, cudaStream_t stream) {
+  if (T_ <= 0) return 0;
+  if (F <= 0 || block < 0 || (block > 0 && F % block != 0)) return CCB_REFUSE_SIZE;
+  const int B = block == 0 ? F : block;
+  const size_t total = (size_t)T_ * F;
+  const int threads = 256;
+  const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+  if (dtype == CCB_F32)
+    ccb_launch(clamped_glu_kernel<float>, blocks, threads, 0, stream, (float*)act, (const float*)gate_up, F, B, total,
+               limit, alpha, up_shift);
+  else if (dtype == CCB_BF16)
+    ccb_launch(clamped_glu_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)act,
+               (const __nv_bfloat16*)gate_up, F, B, total, limit, alpha, up_shift);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}

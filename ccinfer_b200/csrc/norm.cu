@@ -264,3 +264,61 @@ CCB_API int ccb_rmsnorm(void* y, const void* x, const float* w, int rows, int D,
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
 }
+
+// A sublayer's output with a norm of its own, scaled and added to the stream, and the norm that reads the
+// stream next, in one pass over the row:
+//   h <- h + mult * (delta / sqrt(mean(delta^2) + eps_post) * w_post) [+ add];  y = h / sqrt(mean(h^2) + eps_next) * w_next
+// `add` (float [T, D], e.g. the embedding's rows that a repeated pass starts from) and the second norm
+// (w_next, y) are optional.  All sums and the stream are float; delta and y are of the storage type.
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads)
+postnorm_residual_kernel(T* __restrict__ y, float* __restrict__ h, const T* __restrict__ delta,
+                         const float* __restrict__ w_post, float mult, float eps_post, const float* __restrict__ add,
+                         const float* __restrict__ w_next, float eps_next, int D) {
+  ccb::pdl_begin();
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  float* hr = h + (size_t)r * D;
+  const T* dr = delta ? delta + (size_t)r * D : nullptr;
+  const float* ar = add ? add + (size_t)r * D : nullptr;
+  float inv_post = 0.f;
+  if (dr) {
+    float ss = 0.f;
+    for (int d = threadIdx.x; d < D; d += kNormThreads) {
+      const float v = to_f32(dr[d]);
+      ss += v * v;
+    }
+    ss = block_sum<kNormThreads>(ss, red);
+    inv_post = 1.0f / sqrtf(ss / (float)D + eps_post);
+  }
+  float ss2 = 0.f;
+  for (int d = threadIdx.x; d < D; d += kNormThreads) {
+    float v = hr[d];
+    if (dr) v += mult * (to_f32(dr[d]) * inv_post * w_post[d]);
+    if (ar) v += ar[d];
+    if (dr || ar) hr[d] = v;
+    ss2 += v * v;
+  }
+  if (w_next == nullptr) return;
+  ss2 = block_sum<kNormThreads>(ss2, red);
+  const float inv = 1.0f / sqrtf(ss2 / (float)D + eps_next);
+  T* yr = y + (size_t)r * D;
+  for (int d = threadIdx.x; d < D; d += kNormThreads) yr[d] = from_f32<T>(hr[d] * inv * w_next[d]);
+}
+
+CCB_API int ccb_postnorm_residual(void* y, float* h, const void* delta, const float* w_post, float mult,
+                                  float eps_post, const float* add, const float* w_next, float eps_next, int rows,
+                                  int D, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (D <= 0) return CCB_REFUSE_SIZE;
+  if ((delta != nullptr && w_post == nullptr) || (w_next != nullptr && y == nullptr)) return CCB_REFUSE_ARG;
+  if (dtype == CCB_F32)
+    ccb_launch(postnorm_residual_kernel<float>, dim3(rows), dim3(kNormThreads), 0, stream, (float*)y, h,
+               (const float*)delta, w_post, mult, eps_post, add, w_next, eps_next, D);
+  else if (dtype == CCB_BF16)
+    ccb_launch(postnorm_residual_kernel<__nv_bfloat16>, dim3(rows), dim3(kNormThreads), 0, stream, (__nv_bfloat16*)y,
+               h, (const __nv_bfloat16*)delta, w_post, mult, eps_post, add, w_next, eps_next, D);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}

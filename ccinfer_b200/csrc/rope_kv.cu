@@ -7,6 +7,10 @@
 //                                                       (src/kernel/pos/rope.cu:41-46, src/model/rope/rope_cache.cpp:38-45)
 //   Kc[slot, h, :] = k^', Vc[slot, h, :] = v            (src/kernel/attention/write_kv_cache.cu:12-34)
 //
+// Optional, for mixers whose projections have biases and whose queries carry a temperature that grows
+// with the position: x += bias (float, one per output channel of q|k|v, in the kernels' layout) before
+// anything else, and q *= 1 + coef * ln(floor((pos + 1) / every) + 1) after the rotation (every = 0: none).
+//
 // One warp per (token, head); the norm weights and the frequency table are
 // optional (null = that step is left out), so the same kernel serves a mixer
 // without head norms or without rotation.  Cache layout: [page, kv head,
@@ -17,13 +21,24 @@ using namespace ccb;
 
 constexpr int kMaxPairsPerLane = 4;  // head sizes up to 256
 
+struct QkvExtra {
+  const float* bias;  // float [(nq + 2 nkv) * hd] or null
+  float qt_coef;      // query temperature: q *= 1 + qt_coef * ln(floor((pos + 1) / qt_every) + 1)
+  int qt_every;       // 0: no temperature
+};
+
+__device__ __forceinline__ float query_temperature(const QkvExtra& ex, int pos) {
+  if (ex.qt_every <= 0) return 1.0f;
+  return 1.0f + ex.qt_coef * logf((float)((pos + 1) / ex.qt_every) + 1.0f);
+}
+
 template <typename T>
 __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, int row_stride, T* __restrict__ q_out,
                                              T* __restrict__ k_cache, T* __restrict__ v_cache,
                                              const int* __restrict__ positions, const int* __restrict__ slot_map,
                                              const float* __restrict__ inv_freq, const float* __restrict__ q_w,
                                              const float* __restrict__ k_w, float eps, int nq, int nkv, int hd,
-                                             int page_size, int num_slots, int* status) {
+                                             int page_size, int num_slots, QkvExtra ex, int* status) {
   ccb::pdl_begin();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31;
@@ -58,6 +73,10 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, int row_
     if (i < half) {
       x0[m] = to_f32(src[i]);
       x1[m] = to_f32(src[i + half]);
+      if (ex.bias != nullptr) {
+        x0[m] += ex.bias[(size_t)head * hd + i];
+        x1[m] += ex.bias[(size_t)head * hd + i + half];
+      }
       ss += x0[m] * x0[m] + x1[m] * x1[m];
     }
   }
@@ -79,6 +98,7 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, int row_
     inv = 1.0f / sqrtf(ss / (float)hd + eps);
   }
   const float fpos = (float)positions[t];
+  const float qs = is_q ? query_temperature(ex, positions[t]) : 1.0f;
 #pragma unroll
   for (int m = 0; m < kMaxPairsPerLane; ++m) {
     const int i = lane + 32 * m;
@@ -96,8 +116,8 @@ __global__ void qk_norm_rope_kv_write_kernel(const T* __restrict__ qkv, int row_
         a = ra;
         b = rb;
       }
-      dst[i] = from_f32<T>(a);
-      dst[i + half] = from_f32<T>(b);
+      dst[i] = from_f32<T>(a * qs);
+      dst[i + half] = from_f32<T>(b * qs);
     }
   }
 }
@@ -125,7 +145,7 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
                                                  const int* __restrict__ slot_map, const float* __restrict__ inv_freq,
                                                  const float* __restrict__ q_w, const float* __restrict__ k_w,
                                                  float eps, int nq, int nkv, int hd, int page_size, int num_slots,
-                                                 int heads_per_block, int* status) {
+                                                 int heads_per_block, QkvExtra ex, int* status) {
   ccb::pdl_begin();
   constexpr int kIters = 2;  // pairs of elements per lane: head sizes up to 256
   __shared__ float2 cs_table[128];  // (cos, sin) of this token's angles, shared by all heads of the block
@@ -168,6 +188,11 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
     if (i < half) {
       x0[m] = Pair2<T>::load(src + i);
       x1[m] = Pair2<T>::load(src + i + half);
+      if (ex.bias != nullptr) {
+        const float* bh = ex.bias + (size_t)head * hd;
+        x0[m].x += bh[i]; x0[m].y += bh[i + 1];
+        x1[m].x += bh[i + half]; x1[m].y += bh[i + half + 1];
+      }
       ss += x0[m].x * x0[m].x + x0[m].y * x0[m].y + x1[m].x * x1[m].x + x1[m].y * x1[m].y;
     }
   }
@@ -188,6 +213,7 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
     ss = warp_sum(ss);
     inv = 1.0f / sqrtf(ss / (float)hd + eps);
   }
+  const float qs = is_q ? query_temperature(ex, positions[t]) : 1.0f;
 #pragma unroll
   for (int m = 0; m < kIters; ++m) {
     const int i = 2 * lane + 64 * m;
@@ -207,8 +233,8 @@ __global__ void qk_norm_rope_kv_write_vec_kernel(const T* __restrict__ qkv, int 
           b[e] = rb;
         }
       }
-      Pair2<T>::store(dst + i, make_float2(a[0], a[1]));
-      Pair2<T>::store(dst + i + half, make_float2(b[0], b[1]));
+      Pair2<T>::store(dst + i, make_float2(a[0] * qs, a[1] * qs));
+      Pair2<T>::store(dst + i + half, make_float2(b[0] * qs, b[1] * qs));
     }
   }
   }
@@ -223,7 +249,8 @@ qk_norm_rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, int r
                                     __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ positions,
                                     const int* __restrict__ slot_map, const float* __restrict__ inv_freq,
                                     const float* __restrict__ q_w, const float* __restrict__ k_w, float eps, int nq,
-                                    int nkv, int page_size, int num_slots, int heads_per_block, int* status) {
+                                    int nkv, int page_size, int num_slots, int heads_per_block, QkvExtra ex,
+                                    int* status) {
   ccb::pdl_begin();
   constexpr int HD = 16 * LPH, HALF = 8 * LPH, HPW = 32 / LPH;
   __shared__ float2 cs_table[HALF];  // (cos, sin) of this token's angles, shared by all heads of the block
@@ -261,7 +288,7 @@ qk_norm_rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, int r
       ra = *reinterpret_cast<const uint4*>(src + i0);
       rb = *reinterpret_cast<const uint4*>(src + i0 + HALF);
     }
-    if (!is_q && !is_k) {
+    if (!is_q && !is_k && ex.bias == nullptr) {
       if (live) {
         *reinterpret_cast<uint4*>(dst + i0) = ra;
         *reinterpret_cast<uint4*>(dst + i0 + HALF) = rb;
@@ -279,7 +306,17 @@ qk_norm_rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, int r
         b[2 * e] = fb.x; b[2 * e + 1] = fb.y;
       }
     }
-    const float* w = is_q ? q_w : k_w;
+    if (ex.bias != nullptr) {
+      const float* bh = ex.bias + (size_t)head * HD + i0;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        a[e] += bh[e];
+        b[e] += bh[e + HALF];
+      }
+    }
+    const bool plain_v = !is_q && !is_k;  // (with a bias: the sum, written as it is)
+    const float* w = plain_v ? nullptr : (is_q ? q_w : k_w);
+    const float qs = is_q ? query_temperature(ex, positions[t]) : 1.0f;
     float inv = 1.f;
     if (w != nullptr) {
       float ss = 0.f;
@@ -297,13 +334,15 @@ qk_norm_rope_kv_write_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, int r
         a[e] = a[e] * inv * w[i0 + e];
         b[e] = b[e] * inv * w[i0 + e + HALF];
       }
-      if (inv_freq != nullptr) {
+      if (inv_freq != nullptr && !plain_v) {
         const float2 c = cs_table[i0 + e];
         const float xa = a[e] * c.x - b[e] * c.y;
         const float xb = b[e] * c.x + a[e] * c.y;
         a[e] = xa;
         b[e] = xb;
       }
+      a[e] *= qs;
+      b[e] *= qs;
     }
     if (live) {
       uint4 oa, ob;
@@ -324,17 +363,41 @@ template <int LPH>
 static void launch_x8(dim3 grid, cudaStream_t stream, const void* qkv, int row_stride, void* q_out, void* k_cache,
                       void* v_cache, const int* positions, const int* slot_map, const float* inv_freq,
                       const float* q_w, const float* k_w, float eps, int nq, int nkv, int page_size, int num_slots,
-                      int hpb, int* status) {
+                      int hpb, QkvExtra ex, int* status) {
   ccb_launch(qk_norm_rope_kv_write_bf16x8_kernel<LPH>, grid, 128, 0, stream, (const __nv_bfloat16*)qkv, row_stride,
              (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, positions, slot_map, inv_freq,
-             q_w, k_w, eps, nq, nkv, page_size, num_slots, hpb, status);
+             q_w, k_w, eps, nq, nkv, page_size, num_slots, hpb, ex, status);
 }
+
+static int qkv_write(const void* qkv, int row_stride, void* q_out, void* k_cache, void* v_cache,
+                     const int* positions, const int* slot_map, const float* inv_freq, const float* q_w,
+                     const float* k_w, float eps, int T_, int nq, int nkv, int hd, int page_size, int num_slots,
+                     int dtype, QkvExtra ex, int* status, cudaStream_t stream);
 
 CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_out, void* k_cache, void* v_cache,
                                       const int* positions, const int* slot_map, const float* inv_freq,
                                       const float* q_w, const float* k_w, float eps, int T_, int nq, int nkv,
                                       int hd, int page_size, int num_slots, int dtype, int* status,
                                       cudaStream_t stream) {
+  return qkv_write(qkv, row_stride, q_out, k_cache, v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, T_, nq,
+                   nkv, hd, page_size, num_slots, dtype, QkvExtra{nullptr, 0.f, 0}, status, stream);
+}
+
+// The same with the projections' biases and a query temperature (see the head of the file).
+CCB_API int ccb_qkv_bias_rope_kv_write(const void* qkv, int row_stride, void* q_out, void* k_cache, void* v_cache,
+                                       const int* positions, const int* slot_map, const float* inv_freq,
+                                       const float* q_w, const float* k_w, float eps, int T_, int nq, int nkv,
+                                       int hd, int page_size, int num_slots, int dtype, const float* bias,
+                                       float qt_coef, int qt_every, int* status, cudaStream_t stream) {
+  if (qt_every < 0) return CCB_REFUSE_SIZE;
+  return qkv_write(qkv, row_stride, q_out, k_cache, v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, T_, nq,
+                   nkv, hd, page_size, num_slots, dtype, QkvExtra{bias, qt_coef, qt_every}, status, stream);
+}
+
+static int qkv_write(const void* qkv, int row_stride, void* q_out, void* k_cache, void* v_cache,
+                     const int* positions, const int* slot_map, const float* inv_freq, const float* q_w,
+                     const float* k_w, float eps, int T_, int nq, int nkv, int hd, int page_size, int num_slots,
+                     int dtype, QkvExtra ex, int* status, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (hd <= 0 || (hd & 1) || hd > 64 * kMaxPairsPerLane || nq < 0 || nkv < 0 || nq + nkv == 0 || page_size <= 0)
     return CCB_REFUSE_SIZE;
@@ -360,7 +423,7 @@ CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_o
     dim3 g8(T_, (heads + hpb8 - 1) / hpb8);
 #define CCB_X8(L)                                                                                                  \
   launch_x8<L>(g8, stream, qkv, row_stride, q_out, k_cache, v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, \
-               nq, nkv, page_size, num_slots, hpb8, status)
+               nq, nkv, page_size, num_slots, hpb8, ex, status)
     if (lph == 2) CCB_X8(2);
     else if (lph == 4) CCB_X8(4);
     else if (lph == 8) CCB_X8(8);
@@ -371,24 +434,24 @@ CCB_API int ccb_qk_norm_rope_kv_write(const void* qkv, int row_stride, void* q_o
   if (vec && dtype == CCB_F32) {
     ccb_launch(qk_norm_rope_kv_write_vec_kernel<float>, vgrid, 128, 0, stream, (const float*)qkv, row_stride,
                (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, nq, nkv,
-               hd, page_size, num_slots, hpb, status);
+               hd, page_size, num_slots, hpb, ex, status);
     return ccb_launch_status();
   }
   if (vec && dtype == CCB_BF16) {
     ccb_launch(qk_norm_rope_kv_write_vec_kernel<__nv_bfloat16>, vgrid, 128, 0, stream, (const __nv_bfloat16*)qkv,
                row_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, positions,
-               slot_map, inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots, hpb, status);
+               slot_map, inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots, hpb, ex, status);
     return ccb_launch_status();
   }
   if (dtype == CCB_F32)
     ccb_launch(qk_norm_rope_kv_write_kernel<float>, grid, 128, 0, stream, 
         (const float*)qkv, row_stride, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slot_map,
-        inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots, status);
+        inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots, ex, status);
   else if (dtype == CCB_BF16)
     ccb_launch(qk_norm_rope_kv_write_kernel<__nv_bfloat16>, grid, 128, 0, stream, 
         (const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache,
         (__nv_bfloat16*)v_cache, positions, slot_map, inv_freq, q_w, k_w, eps, nq, nkv, hd, page_size, num_slots,
-        status);
+        ex, status);
   else
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();

@@ -128,8 +128,14 @@ class Engine:
                 token_bytes[g] += need.bytes_per_token(self.dtype)
                 owners[i] = need
             sn = mixer.state_need()
-            if sn is not None:
-                self._state[i] = torch.zeros((opt.max_requests,) + tuple(sn.shape), dtype=sn.dtype, device=rt.device)
+            if isinstance(sn, (list, tuple)):   # several named tensors: the mixer gets a dict
+                if len({n.name for n in sn}) != len(sn) or not sn:
+                    raise InvalidArgument(f"order[{i}]: a list of state needs names at least one tensor, each once")
+                self._state[i] = {n.name: torch.zeros((opt.max_requests,) + tuple(n.shape),
+                                                      dtype=n.dtype or self.dtype, device=rt.device) for n in sn}
+            elif sn is not None:
+                self._state[i] = torch.zeros((opt.max_requests,) + tuple(sn.shape), dtype=sn.dtype or self.dtype,
+                                             device=rt.device)
         for i, e in enumerate(plan.order):
             if e.cache_of is not None:
                 if e.cache_of not in self._entry_group:
@@ -263,7 +269,8 @@ class Engine:
         """Gives the request a state slot (its state tensors are zeroed); returns the slot."""
         rc = self.cache.open(req_id)
         for st in self._state.values():
-            st[rc.slot].zero_()
+            for t in (st.values() if isinstance(st, dict) else (st,)):
+                t[rc.slot].zero_()
         return rc.slot
 
     def close_request(self, req_id: Hashable) -> None:
@@ -411,6 +418,12 @@ class Engine:
             stream = plan.embedding.forward(step, getattr(plan.layers[plan.order[0].layer], "first_norm", None))
         else:
             stream = plan.embedding.forward(step)
+        first_rows = None
+        if any(e.add_embedding for e in plan.order):
+            # a repeated pass starts from its input plus the embedding's rows: they are kept beside the stream
+            first_rows = self.rt.scratch.get("embedding_rows", (self.rt.max_tokens, stream.h.shape[1]),
+                                             torch.float32)[:step.n_tokens]
+            first_rows.copy_(stream.h)
         for i, e in enumerate(plan.order):
             block = plan.layers[e.layer]
             cache = None
@@ -419,7 +432,11 @@ class Engine:
                 cache = LayerCache(self._cache[src], step.groups[self._entry_group[i]], own=e.cache_of is None)
             nxt = plan.layers[plan.order[i + 1].layer] if i + 1 < len(plan.order) else None
             stream.next_norm = getattr(nxt, "first_norm", None)
+            stream.next_add = first_rows if nxt is not None and plan.order[i + 1].add_embedding else None
             block.forward(stream, step, cache, self._state.get(i))
+            if stream.next_add is not None:   # the block left the addition to us (it commutes with a pending sum)
+                kernels.postnorm_residual(stream.h, None, None, 0.0, 0.0, add=stream.next_add)
+                stream.next_add = stream.ready = stream.unscaled = None
         if step.n_logit_rows == 0:
             return None
         x = plan.final_norm.fold(stream, rows=step.logit_rows, n_rows=step.n_logit_rows)

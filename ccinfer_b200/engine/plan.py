@@ -14,10 +14,13 @@ class RunEntry:
     ``layer`` indexes ``ModelPlan.layers``; naming a layer in two entries runs
     its weights twice, each run with a cache of its own.  ``cache_of`` names an
     earlier entry of the order whose cache this run reads instead of keeping
-    one (its mixer then writes no keys or values).
+    one (its mixer then writes no keys or values).  ``add_embedding``: before
+    this run the embedding's rows are added to the stream once more (the first
+    layer of a repeated pass over some layers).
     """
     layer: int
     cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclasses.dataclass
@@ -56,6 +59,8 @@ class ModelPlan:
         for i, e in enumerate(self.order):
             if not (0 <= e.layer < len(self.layers)):
                 raise ValueError(f"order[{i}] names layer {e.layer}, the model has {len(self.layers)}")
+            if e.add_embedding and i == 0:
+                raise ValueError("order[0] cannot add the embedding's rows: the stream holds nothing else yet")
             if e.cache_of is not None:
                 if not (0 <= e.cache_of < i):
                     raise ValueError(f"order[{i}] reads the cache of entry {e.cache_of}, which does not run before it")

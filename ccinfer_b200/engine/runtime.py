@@ -139,11 +139,22 @@ class Runtime:
         self.cublas.gemm_bf16(out, x, w)
         return out
 
-    def gated_up(self, act: torch.Tensor, x: torch.Tensor, w: torch.Tensor, block: int) -> torch.Tensor:
+    def gated_up(self, act: torch.Tensor, x: torch.Tensor, w: torch.Tensor, block: int, activation=None) -> torch.Tensor:
         """act[M, F] = silu(x Wg^T) * (x Wu^T) for the merged weight w [2F, K] (``block``: see kernels.silu_mul).
 
         A few tokens in bfloat16 with the blocked layout: one kernel (the activation is the product's
-        epilogue).  Otherwise the product into scratch and the activation kernel."""
+        epilogue).  Otherwise the product into scratch and the activation kernel.
+        ``activation`` ("clamped_glu", limit, alpha, shift): that activation in place of silu(g) * u; the
+        product's epilogues know silu only, so it is always a kernel of its own."""
+        if activation is not None:
+            x = self.rows(x)
+            gu = self.scratch.get("ffn_gate_up", (self.max_tokens, w.shape[0]), self.dtype)[:x.shape[0]]
+            self.linear(gu, x, w)
+            kind, limit, alpha, shift = activation
+            if kind != "clamped_glu":
+                raise Unsupported(f"gated activation {kind!r}")
+            kernels.clamped_glu(act, gu, block, limit, alpha, shift)
+            return act
         un = x if isinstance(x, UnscaledRows) else None
         if un is not None:
             x = un.x

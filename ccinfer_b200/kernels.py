@@ -55,6 +55,21 @@ _SIGNATURES = {
     "ccb_qk_norm_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                   c_void_p, c_void_p],
+    "ccb_qkv_bias_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                   c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_float, c_int, c_void_p, c_void_p],
+    "ccb_postnorm_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p, c_float,
+                              c_int, c_int, c_int, c_void_p],
+    "ccb_clamped_glu": [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_int, c_void_p],
+    "ccb_delta_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                          c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
+    "ccb_conv_state_update": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                              c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_delta_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_gated_head_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int,
+                               c_void_p],
     "ccb_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                     c_void_p, c_void_p],
@@ -291,6 +306,105 @@ def qk_norm_rope_kv_write(qkv, q_out, k_cache, v_cache, positions, slot_map, inv
                                            _p(positions), _p(slot_map), _p(inv_freq), _p(q_w), _p(k_w),
                                            float(eps), T, nq, nkv, hd, page_size, num_slots, _dt(qkv),
                                            _p(status), _stream()), "qk_norm_rope_kv_write")
+
+
+def qkv_bias_rope_kv_write(qkv, q_out, k_cache, v_cache, positions, slot_map, inv_freq, q_w, k_w, eps,
+                           nq: int, nkv: int, hd: int, page_size: int, bias=None, q_temperature=None,
+                           status=None) -> None:
+    """qk_norm_rope_kv_write for projections with biases and queries with a temperature.
+
+    ``bias`` float [(nq + 2 nkv) * hd] is added to the rows of qkv before anything else;
+    ``q_temperature = (coef, every)``: q *= 1 + coef * ln(floor((pos + 1) / every) + 1) after the rotation."""
+    _cuda(qkv, q_out, k_cache, v_cache, positions, slot_map, inv_freq, q_w, k_w, bias, status)
+    T = q_out.shape[0]
+    assert qkv.shape[0] >= T and qkv.shape[1] >= (nq + 2 * nkv) * hd and qkv.dtype == q_out.dtype
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == (nq + 2 * nkv) * hd)
+    num_slots = 0
+    if nkv > 0:
+        assert k_cache.dtype == qkv.dtype and v_cache.dtype == qkv.dtype
+        assert k_cache.shape[1:] == (nkv, page_size, hd) and v_cache.shape == k_cache.shape
+        num_slots = k_cache.shape[0] * page_size
+    coef, every = q_temperature if q_temperature is not None else (0.0, 0)
+    _check(lib().ccb_qkv_bias_rope_kv_write(_p(qkv), qkv.stride(0), _p(q_out), _p(k_cache), _p(v_cache),
+                                            _p(positions), _p(slot_map), _p(inv_freq), _p(q_w), _p(k_w),
+                                            float(eps), T, nq, nkv, hd, page_size, num_slots, _dt(qkv), _p(bias),
+                                            float(coef), int(every), _p(status), _stream()),
+           "qkv_bias_rope_kv_write")
+
+
+def postnorm_residual(h, delta, w_post, mult: float, eps_post: float, add=None, y=None, w_next=None,
+                      eps_next: float = 0.0) -> None:
+    """h += mult * RMSNorm(delta; w_post) [+ add]; with ``w_next``, y = RMSNorm(h; w_next) in the same pass.
+
+    h and add float [T, D]; delta and y in the storage type; the weights float [D].  ``delta`` None: only the
+    addition of ``add`` and/or the second norm."""
+    _cuda(h, delta, w_post, add, y, w_next)
+    T, D = h.shape
+    assert h.dtype == torch.float32 and (delta is None or (delta.shape == (T, D) and w_post.numel() == D))
+    assert add is None or (add.dtype == torch.float32 and add.shape[1] == D and add.shape[0] >= T)
+    assert w_next is None or (y is not None and y.shape == (T, D) and w_next.numel() == D)
+    assert delta is None or y is None or delta.dtype == y.dtype
+    ref = delta if delta is not None else y
+    _check(lib().ccb_postnorm_residual(_p(y), _p(h), _p(delta), _p(w_post), float(mult), float(eps_post), _p(add),
+                                       _p(w_next), float(eps_next), T, D, _dt(ref) if ref is not None else F32,
+                                       _stream()), "postnorm_residual")
+
+
+def clamped_glu(act, gate_up, block: int, limit: float, alpha: float, up_shift: float) -> None:
+    """act = g * sigmoid(alpha g) * (u + up_shift) with g = min(gate, limit), u = clamp(up, -limit, limit);
+    the layouts of gate_up are those of ``silu_mul``."""
+    _cuda(act, gate_up)
+    T, F = act.shape
+    assert gate_up.shape == (T, 2 * F) and act.dtype == gate_up.dtype
+    _check(lib().ccb_clamped_glu(_p(act), _p(gate_up), T, F, int(block), float(limit), float(alpha),
+                                 float(up_shift), _dt(act), _stream()), "clamped_glu")
+
+
+def delta_prepare(proj, offsets, a, conv_w, taps: int, conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot,
+                  qn, kn, vv, gg, bb, G: int, H: int, dk: int, dv: int, q_mult: float, unit_eps: float) -> None:
+    """The inputs of the gated delta rule from the projections' rows: convolution + silu of q, k, v (with the
+    request's convolution state before the portion), unit q and k per head (q times ``q_mult``),
+    beta = sigmoid(b), decay = exp(-exp(A_log) softplus(a + dt_bias)); outputs float.  ``offsets`` = the first
+    columns of q, k, v, b in ``proj``."""
+    _cuda(conv_w, conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, qn, kn, vv, gg, bb)
+    T = qn.shape[0]
+    assert proj.stride(1) == 1 and a.stride(1) == 1 and proj.dtype == a.dtype == conv_state.dtype
+    assert conv_w.dtype == torch.float32 and conv_w.shape == (2 * G * dk + H * dv, taps)
+    oq, ok, ov, ob = offsets
+    _check(lib().ccb_delta_prepare(_p(proj), proj.stride(0), oq, ok, ov, ob, _p(a), a.stride(0), _p(conv_w), taps,
+                                   _p(conv_state), _p(A_log), _p(dt_bias), _p(entry_of_token), _p(cu_q),
+                                   _p(state_slot), _p(qn), _p(kn), _p(vv), _p(gg), _p(bb), T, G, H, dk, dv,
+                                   float(q_mult), float(unit_eps), _dt(proj), _stream()), "delta_prepare")
+
+
+def conv_state_update(proj, offsets, conv_state, taps: int, cu_q, state_slot, n_entries: int, G: int, H: int,
+                      dk: int, dv: int) -> None:
+    """The last taps - 1 rows of q|k|v of each request's portion become its convolution state."""
+    _cuda(conv_state, cu_q, state_slot)
+    oq, ok, ov, _ = offsets
+    _check(lib().ccb_conv_state_update(_p(proj), proj.stride(0), oq, ok, ov, _p(conv_state), taps, _p(cu_q),
+                                       _p(state_slot), n_entries, G, H, dk, dv, _dt(proj), _stream()),
+           "conv_state_update")
+
+
+def delta_recurrence(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries: int, G: int, H: int, dk: int,
+                     dv: int) -> None:
+    """The gated delta rule over each request's tokens of the step, from and into ``state``
+    [slots, H, dv, dk] (float); out float [T, H, dv]."""
+    _cuda(qn, kn, vv, gg, bb, state, out, cu_q, state_slot)
+    assert state.dtype == torch.float32 and state.shape[1:] == (H, dv, dk) and out.dtype == torch.float32
+    _check(lib().ccb_delta_recurrence(_p(qn), _p(kn), _p(vv), _p(gg), _p(bb), _p(state), _p(out), _p(cu_q),
+                                      _p(state_slot), n_entries, G, H, dk, dv, _stream()), "delta_recurrence")
+
+
+def gated_head_rmsnorm(y, o, gate, w, H: int, dv: int, eps: float) -> None:
+    """y[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * sigmoid(gate[t, h, :]); o float, gate and y storage type."""
+    _cuda(y, o, w)
+    T = y.shape[0]
+    assert o.dtype == torch.float32 and w.dtype == torch.float32 and w.numel() == dv and gate.stride(1) == 1
+    assert gate.dtype == y.dtype
+    _check(lib().ccb_gated_head_rmsnorm(_p(y), _p(o), _p(gate), gate.stride(0), _p(w), T, H, dv, float(eps),
+                                        _dt(y), _stream()), "gated_head_rmsnorm")
 
 
 def paged_attention_generic(q, k_cache, v_cache, out, positions, entry_of_token, block_table, n_entries: int,

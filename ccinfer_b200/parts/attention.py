@@ -13,6 +13,16 @@ o projections (and must use the position encoding of the layer whose keys it
 reads).  Head sizes are multiples of 16 up to 256: others are refused (the
 reference's decode kernel takes any head size up to 128,
 src/kernel/attention/decode_attn.cu:521-569).
+
+Beyond the reference: biases of the three projections (names q_bias, k_bias,
+v_bias; added by the kernel that rotates q and k and writes the cache), a
+value size that differs from the query/key size (``value_dim``), a score scale
+of the model's choosing, and a query temperature stated by the position
+encoding.  The attention kernels know one head size; with ``value_dim`` given,
+the heads of q, k and v are laid out in the smallest size the kernels take that
+holds both (a multiple of 16), the added coordinates being zero rows of the
+projections and zero columns of the output projection: zeros in q and k add
+nothing to a score, zeros in v give zeros that the output projection ignores.
 """
 from __future__ import annotations
 
@@ -31,10 +41,21 @@ class GroupedQueryAttention(Mixer):
 
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PositionEncoding, names: dict, qk_norm_eps: Optional[float] = None,
-                 window: Optional[int] = None, own_kv: bool = True, scale: Optional[float] = None):
-        """``names``: tensor names under the keys q, k, v, o and (with qk_norm_eps) q_norm, k_norm."""
+                 window: Optional[int] = None, own_kv: bool = True, scale: Optional[float] = None,
+                 value_dim: Optional[int] = None, float_weights: bool = False):
+        """``names``: tensor names under the keys q, k, v, o and (with qk_norm_eps) q_norm, k_norm; with
+        q_bias, k_bias, v_bias the projections have biases.  ``value_dim``: size of a value head where it is
+        not ``head_dim``; the position encoding is then built for ``kernel_head_dim(head_dim, value_dim)``.
+        ``float_weights``: the softmax weights stay float up to their product with the values (every row
+        goes to the split kernel; the tensor-core kernels round them to bfloat16 for that product)."""
         if num_heads % num_kv_heads:
             raise Unsupported(f"{num_heads} heads are not a multiple of {num_kv_heads} kv heads")
+        self.qk_dim = int(head_dim)
+        self.v_dim = int(head_dim if value_dim is None else value_dim)
+        if value_dim is not None:
+            head_dim = self.kernel_head_dim(head_dim, value_dim)
+            if qk_norm_eps is not None and head_dim != self.qk_dim:
+                raise Unsupported("per-head q/k norms over heads that are laid out in a larger size")
         if head_dim % 16 or head_dim > 256:
             raise Unsupported(f"head size {head_dim}: the attention kernels take multiples of 16 up to 256")
         if window is not None and window <= 0:
@@ -42,17 +63,30 @@ class GroupedQueryAttention(Mixer):
         self.hidden, self.nq, self.nkv, self.hd = int(hidden), int(num_heads), int(num_kv_heads), int(head_dim)
         self.position, self.names = position, dict(names)
         self.qk_norm_eps, self.window, self.own_kv = qk_norm_eps, window, own_kv
-        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
+        self.has_bias = "q_bias" in self.names
+        self.float_weights = bool(float_weights)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.qk_dim)
         self.q_width, self.kv_width = self.nq * self.hd, self.nkv * self.hd
+        self.bias = None
         self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
         self.rt = None
+
+    @staticmethod
+    def kernel_head_dim(head_dim: int, value_dim: int) -> int:
+        """The head size the kernels run with for these query/key and value sizes."""
+        return -(-max(int(head_dim), int(value_dim)) // 16) * 16
 
     # -- what it wants ---------------------------------------------------------
     def tensor_specs(self):
         n, D = self.names, self.hidden
-        specs = [TensorSpec(n["q"], (self.q_width, D)), TensorSpec(n["o"], (D, self.q_width))]
+        specs = [TensorSpec(n["q"], (self.nq * self.qk_dim, D)), TensorSpec(n["o"], (D, self.nq * self.v_dim))]
         if self.own_kv:
-            specs += [TensorSpec(n["k"], (self.kv_width, D)), TensorSpec(n["v"], (self.kv_width, D))]
+            specs += [TensorSpec(n["k"], (self.nkv * self.qk_dim, D)), TensorSpec(n["v"], (self.nkv * self.v_dim, D))]
+        if self.has_bias:
+            specs.append(TensorSpec(n["q_bias"], (self.nq * self.qk_dim,), role="vector"))
+            if self.own_kv:
+                specs += [TensorSpec(n["k_bias"], (self.nkv * self.qk_dim,), role="vector"),
+                          TensorSpec(n["v_bias"], (self.nkv * self.v_dim,), role="vector")]
         if self.qk_norm_eps is not None:
             specs.append(TensorSpec(n["q_norm"], (self.hd,), role="vector", init="one_plus_normal"))
             if self.own_kv:
@@ -88,12 +122,34 @@ class GroupedQueryAttention(Mixer):
 
             def heads(w, n_heads):
                 return w
+        hd = self.hd
+
+        def laid_out(w, n_heads, d):
+            """[n_heads * d, ...] -> [n_heads * hd, ...]: each head's rows followed by zero rows up to hd."""
+            if d == hd:
+                return w
+            w = w.view(n_heads, d, -1)
+            out = torch.zeros((n_heads, hd, w.shape[2]), dtype=w.dtype, device=w.device)
+            out[:, :d] = w
+            return out.view(n_heads * hd, -1)
+
+        def qk(name, n_heads):
+            return heads(laid_out(fetch(n[name]), n_heads, self.qk_dim), n_heads)
+
         if self.own_kv:
-            self.w_qkv = torch.cat([heads(fetch(n["q"]), self.nq), heads(fetch(n["k"]), self.nkv), fetch(n["v"])],
+            self.w_qkv = torch.cat([qk("q", self.nq), qk("k", self.nkv), laid_out(fetch(n["v"]), self.nkv, self.v_dim)],
                                    dim=0).contiguous()
         else:
-            self.w_qkv = heads(fetch(n["q"]), self.nq).contiguous()
-        self.w_o = fetch(n["o"])
+            self.w_qkv = qk("q", self.nq).contiguous()
+        if self.has_bias:
+            parts = [qk("q_bias", self.nq)]
+            if self.own_kv:
+                parts += [qk("k_bias", self.nkv), laid_out(fetch(n["v_bias"]), self.nkv, self.v_dim)]
+            self.bias = torch.cat([p.reshape(-1) for p in parts]).float().contiguous()
+        w_o = fetch(n["o"])
+        if self.v_dim != hd:   # zero columns where the heads of o carry the added coordinates
+            w_o = laid_out(w_o.t().contiguous(), self.nq, self.v_dim).t().contiguous()
+        self.w_o = w_o
         if self.qk_norm_eps is not None:
             self.q_norm_w = fetch(n["q_norm"])
             self.k_norm_w = fetch(n["k_norm"]) if self.own_kv else None
@@ -109,7 +165,8 @@ class GroupedQueryAttention(Mixer):
         a prefill kernel (tcgen05 with 128 query tokens a block, or mma.sync with 64); otherwise every row is
         a single query of the split kernel, which takes all sizes and both types."""
         rt, g = self.rt, cache.group
-        mma = rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
+        mma = (rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
+               and not self.float_weights)
         n_rows = step.n_single if mma else T
         if n_rows > 0:
             per_block = kernels.DECODE_MMA_HEADS_PER_BLOCK if mma else 0
@@ -142,7 +199,8 @@ class GroupedQueryAttention(Mixer):
         """A step of single tokens only, on the path of the TMA decode kernel (bfloat16, head size 64 or 128,
         a page size it takes), with few enough rows that every block redoing the queries' norm and rotation
         costs less than a kernel of its own."""
-        return (self.rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
+        return (self.bias is None and self.position.query_temperature() is None and not self.float_weights
+                and self.rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
                 and kernels.attention_decode_tma_fits(self.hd, g.page_size)
                 and step.n_single == step.n_entries == step.n_tokens
                 and step.n_tokens <= self.FUSED_DECODE_MAX_ROWS)
@@ -171,11 +229,14 @@ class GroupedQueryAttention(Mixer):
                 merge_counters=rt.merge_counters if splits >= self.MERGE_IN_KERNEL_MIN_SPLITS else None)
         else:
             q = rt.scratch.get("attn_q", (rt.max_tokens, self.nq, self.hd), rt.dtype)[:T]
-            kernels.qk_norm_rope_kv_write(
-                qkv, q, cache.k if self.own_kv else None, cache.v if self.own_kv else None, step.positions,
-                g.slot_map if self.own_kv else None, self.position.rotary_table(), self.q_norm_w, self.k_norm_w,
-                self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, self.nq, nkv_w, self.hd, g.page_size,
-                status=rt.status)
+            args = (qkv, q, cache.k if self.own_kv else None, cache.v if self.own_kv else None, step.positions,
+                    g.slot_map if self.own_kv else None, self.position.rotary_table(), self.q_norm_w, self.k_norm_w,
+                    self.qk_norm_eps if self.qk_norm_eps is not None else 1.0, self.nq, nkv_w, self.hd, g.page_size)
+            q_temp = self.position.query_temperature()
+            if self.bias is not None or q_temp is not None:
+                kernels.qkv_bias_rope_kv_write(*args, bias=self.bias, q_temperature=q_temp, status=rt.status)
+            else:
+                kernels.qk_norm_rope_kv_write(*args, status=rt.status)
             self._attend(q, o, cache, step, T)
         out = rt.scratch.get("attn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
         return rt.linear(out, o.view(T, self.q_width), self.w_o, sink=step.take_sink())

@@ -95,9 +95,14 @@ class CacheNeed:
 
 @dataclasses.dataclass(frozen=True)
 class StateNeed:
-    """A tensor of fixed shape per request (zeroed when a request gets its slot)."""
+    """A tensor of fixed shape per request (zeroed when a request gets its slot).
+
+    A mixer that keeps several returns a list of them from ``state_need()``, each with a ``name``; its
+    ``forward`` then gets a dict name -> [max_requests, *shape] tensor instead of one tensor.
+    ``dtype`` None: the engine's compute type."""
     shape: Tuple[int, ...]
-    dtype: torch.dtype = torch.float32
+    dtype: Optional[torch.dtype] = torch.float32
+    name: str = "state"
 
 
 class Part:
@@ -132,6 +137,10 @@ class Residual:
         self.next_norm = None
         # (norm, rows): the rows of ``norm`` are there already (the embedding wrote them with the stream)
         self.ready = None
+        # float [T, D] rows that are to be added to ``h`` before the next block reads it (a repeated pass
+        # over some layers starts from its input plus the embedding's rows).  A block that adds them itself
+        # (in the kernel of its last sum) clears this; otherwise the engine does the addition.
+        self.next_add: Optional[torch.Tensor] = None
 
 
 class UnscaledRows:
@@ -202,6 +211,10 @@ class PositionEncoding(Part):
         return None
 
     def score_bias(self):
+        return None
+
+    def query_temperature(self):
+        """(coef, every) if queries are scaled by 1 + coef * ln(floor((pos + 1) / every) + 1), else None."""
         return None
 
 

@@ -9,6 +9,11 @@ norm after it needs no kernel (``parts.base.UnscaledRows``).
 """
 from __future__ import annotations
 
+from typing import Optional
+
+import torch
+
+from .. import kernels
 from .base import Block, FeedForward, Mixer, Norm, Residual, ResidualSink
 
 
@@ -44,3 +49,68 @@ class PreNormBlock(Block):
         stream.pending = self.ffn.forward(x, step)
         step.residual_sink = None
         stream.takes_unscaled = False
+
+
+class SandwichNormBlock(Block):
+    """A norm before AND after each sublayer, the normed output scaled by a constant before the sum:
+
+        h += mult * post1(Mixer(norm1(h)));   h += mult * post2(FeedForward(norm2(h)))
+
+    The feed-forward (with norm2 and post2) may be absent.  All four are RMS norms with the same eps.  The
+    sum, the norm of the sublayer's output and the norm that reads the stream next are one kernel
+    (``kernels.postnorm_residual``): it also takes the rows that a repeated pass adds to the stream
+    (``Residual.next_add``) and leaves the next block's first norm as ``stream.ready``."""
+
+    def __init__(self, norm1, mixer: Mixer, post1, norm2=None, ffn: Optional[FeedForward] = None, post2=None,
+                 mult: float = 1.0):
+        if (ffn is None) != (norm2 is None) or (ffn is None) != (post2 is None):
+            raise ValueError("a feed-forward comes with its two norms, or none of the three is given")
+        self.norm1, self.mixer, self.post1, self.norm2, self.ffn, self.post2 = norm1, mixer, post1, norm2, ffn, post2
+        self.mult = float(mult)
+        self.rt = None
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.post1, self.norm2, self.ffn, self.post2) if p is not None]
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self._parts())
+
+    def tensor_specs(self):
+        return [s for p in self._parts() for s in p.tensor_specs()]
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+        for p in self._parts():
+            p.bind(rt, fetch)
+
+    @property
+    def first_norm(self):
+        return self.norm1
+
+    def _sum(self, stream: Residual, delta, post, nxt, last: bool):
+        """h += mult * post(delta) (+ the rows a repeated pass adds, after the block's last sum); with
+        ``nxt`` its rows are returned."""
+        rt = self.rt
+        add = None
+        if last and stream.next_add is not None:
+            add, stream.next_add = stream.next_add, None
+        y = None
+        usable = nxt is not None and hasattr(nxt, "w") and hasattr(nxt, "eps")
+        if usable:
+            y = rt.scratch.get(nxt.scratch_key, (rt.max_tokens, nxt.dim), rt.dtype)[:stream.h.shape[0]]
+        kernels.postnorm_residual(stream.h, rt.rows(delta), post.w, self.mult, post.eps, add=add,
+                                  y=y, w_next=nxt.w if usable else None, eps_next=nxt.eps if usable else 0.0)
+        return y
+
+    def forward(self, stream: Residual, step, cache, state) -> None:
+        after = stream.next_norm
+        stream.takes_unscaled = False
+        x = self.norm1.fold(stream)
+        step.residual_sink = None
+        a = self.mixer.forward(x, step, cache, state)
+        x = self._sum(stream, a, self.post1, self.norm2 if self.ffn is not None else after, self.ffn is None)
+        if self.ffn is not None:
+            m = self.ffn.forward(x, step)
+            x = self._sum(stream, m, self.post2, after, True)
+        stream.ready = (after, x) if (after is not None and x is not None) else None

@@ -17,6 +17,7 @@ from .base import FeedForward, TensorSpec
 
 class SwiGLU(FeedForward):
     takes_unscaled = True
+    activation = None   # silu(gate) * up; a subclass names another one (see Runtime.gated_up)
 
     def __init__(self, hidden: int, intermediate: int, names: dict):
         """``names``: tensor names under the keys gate, up, down."""
@@ -43,6 +44,18 @@ class SwiGLU(FeedForward):
         rt = self.rt
         T = x.shape[0]
         act = rt.scratch.get("ffn_act", (rt.max_tokens, self.inter), rt.dtype)[:T]
-        rt.gated_up(act, x, self.w_gate_up, self.block)
+        rt.gated_up(act, x, self.w_gate_up, self.block, activation=self.activation)
         out = rt.scratch.get("ffn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
         return rt.linear(out, act, self.w_down, sink=step.take_sink())
+
+
+class ClampedGLU(SwiGLU):
+    """The same two products with clamped inputs and a sigmoid gate of its own slope:
+
+        g = min(x Wg^T, limit), u = clamp(x Wu^T, -limit, limit);  m = (g * sigmoid(alpha g) * (u + shift)) Wd^T
+    """
+
+    def __init__(self, hidden: int, intermediate: int, names: dict, limit: float, alpha: float = 1.702,
+                 shift: float = 1.0):
+        super().__init__(hidden, intermediate, names)
+        self.activation = ("clamped_glu", float(limit), float(alpha), float(shift))

@@ -39,8 +39,15 @@ class RotaryHalf(PositionEncoding):
     kernels' layout plus a table with zeros for the pairs that do not turn (see PositionEncoding).
     """
 
-    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, interleaved: bool = False):
+    def __init__(self, head_dim: int, theta: float, rotary_dim: int = None, interleaved: bool = False,
+                 linear_scaling: float = None, query_temperature=None):
+        """``linear_scaling`` s: every frequency is divided by s (positions are stretched by s); the table is
+        then evaluated in float64 and rounded once.  ``query_temperature``: see ``QueryTemperature``."""
         rotary_dim = int(head_dim if rotary_dim is None else rotary_dim)
+        if linear_scaling is not None and not (linear_scaling > 0):
+            raise ValueError("linear_scaling must be > 0")
+        self.linear_scaling = None if linear_scaling is None else float(linear_scaling)
+        self._q_temp = query_temperature
         if head_dim % 2 or rotary_dim % 2 or not (0 < rotary_dim <= head_dim):
             raise ValueError(f"rotation of {rotary_dim} of {head_dim} coordinates: both even, 0 < rotary_dim <= head_dim")
         self.head_dim, self.theta, self.rotary_dim, self.interleaved = int(head_dim), float(theta), rotary_dim, interleaved
@@ -50,11 +57,19 @@ class RotaryHalf(PositionEncoding):
     def bind(self, rt, fetch):
         self.rt = rt
         table = np.zeros(self.head_dim // 2, dtype=np.float32)
-        table[:self.rotary_dim // 2] = rotary_inv_freq(self.rotary_dim, self.theta)
+        if self.linear_scaling is None:
+            table[:self.rotary_dim // 2] = rotary_inv_freq(self.rotary_dim, self.theta)
+        else:
+            i = np.arange(self.rotary_dim // 2, dtype=np.float64)
+            table[:self.rotary_dim // 2] = (np.power(np.float64(self.theta), -2.0 * i / self.rotary_dim)
+                                            / self.linear_scaling).astype(np.float32)
         self.inv_freq = torch.from_numpy(table).to(rt.device)
 
     def rotary_table(self):
         return self.inv_freq
+
+    def query_temperature(self):
+        return self._q_temp
 
     def head_permutation(self):
         hd, rd, half = self.head_dim, self.rotary_dim, self.head_dim // 2
@@ -91,3 +106,20 @@ class NoPosition(PositionEncoding):
 
     def rotary_table(self):
         return None
+
+
+class QueryTemperature(PositionEncoding):
+    """No rotation; the position enters through the length of the query alone:
+    q_p <- q_p * (1 + coef * ln(floor((p + 1) / every) + 1)), so that scores sharpen as the context grows
+    in steps of ``every`` tokens.  Evaluated in float by the kernel that writes q."""
+
+    def __init__(self, coef: float, every: int):
+        if int(every) <= 0:
+            raise ValueError("query temperature: 'every' must be a positive number of tokens")
+        self.coef, self.every = float(coef), int(every)
+
+    def rotary_table(self):
+        return None
+
+    def query_temperature(self):
+        return (self.coef, self.every)
