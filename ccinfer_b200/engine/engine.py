@@ -459,13 +459,19 @@ class Engine:
         touches has a fixed address (the small layout's device buffer, the scratch pool), so it is captured
         once per size (rows beyond the live requests are padding: they cache nothing and attend to nothing)."""
         if bucket not in self._graphs:
-            self._forward(step)  # once eagerly: every scratch buffer exists before the capture ...
+            eager = self._forward(step)  # once eagerly: every scratch buffer exists before the capture ...
             self.rt.scratch.freeze()  # ... and none may move once a graph holds its address
             graph = torch.cuda.CUDAGraph()
             own0, lib0 = kernels.counters.own, kernels.counters.library
             with torch.cuda.graph(graph):
                 out = self._forward(step)
             self._graphs[bucket] = (graph, out, kernels.counters.own - own0, kernels.counters.library - lib0)
+            if self._state:
+                # the eager run WAS this step: keys and values may be written twice, a state that is carried
+                # from token to token must not be advanced twice.  The capture ran nothing and its logits are
+                # the eager run's buffer.
+                assert eager.data_ptr() == out.data_ptr()
+                return eager[:n_real]
         graph, out, n_own, n_lib = self._graphs[bucket]
         graph.replay()
         kernels.counters.own += n_own      # a replay launches what the capture recorded
