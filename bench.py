@@ -34,6 +34,14 @@ every kernel) and, with --profile-prefill T, one prompt of T tokens in one step;
 runs one of the two other workloads of the reference's benchmark record through the scheduler (a mixed
 continuous batch at the Qwen3-14B shape; four 16,384-token prompts at the Qwen3-32B shape) and prints a
 line of its own: output tokens a second, the distribution of the step calls, the pages' high water.
+
+    python bench.py --design tugelorn [--design-sizes mid,8b] [--layers L] [--design-profile]
+
+measures another design of the package beside Qwen3 at equal layer sizes (same width, heads, head size,
+intermediate size, vocabulary and number of layers; random weights): one prompt of 2,048 and of 8,192 tokens
+in steps of 2,048 (tokens a second) and decode steps of 1 and 8 requests after 2,048-token prompts, replayed
+from CUDA graphs (tokens a second), one JSON line per size.  With --design-profile it only runs a prompt and a
+few eager decode steps of the design, for profilers.  The default line and its contract are untouched.
 """
 import argparse
 import json
@@ -258,6 +266,131 @@ def run_profile_steps(args) -> int:
     return 0
 
 
+DESIGN_SIZES = {
+    # name: width, q heads, kv heads, head size, intermediate, vocabulary
+    "mid": (2048, 16, 8, 128, 8192, 32000),
+    "8b": (4096, 32, 8, 128, 12288, 151936),
+}
+
+
+def tugelorn_config(size: str, layers: int):
+    """Layers in turn: windowed rotary attention, gated delta rule, attention with biases and a query
+    temperature; each with a feed-forward; the middle third of the layers runs twice."""
+    from ccinfer_b200.config.tugelorn import TugelornConfig
+    D, H, G, hd, F, V = DESIGN_SIZES[size]
+    kinds = [
+        {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                                        "mask": {"size": 1024},
+                                        "rot": {"dims": hd, "base": 500000.0, "scaling": {"factor": 8.0}}}},
+        {"type": "channel_delta", "mixer": {"heads": H, "kv_heads": H, "dim": hd, "vdim": hd, "conv": 4,
+                                            "a_rank": hd, "g_rank": hd}},
+        {"type": "attention_2", "mixer": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                                          "q_temp": {"coef": 0.1, "every": 1024}}},
+    ]
+    mlp = {"kind": "dense", "ff": F, "limit": 7.0}
+    j = {"architecture": "Tugelorn", "vocab": V, "width": D, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+         "layers": [dict(kinds[i % 3], mlp=mlp) for i in range(layers)]}
+    return TugelornConfig.from_json(j)
+
+
+def run_design(args) -> int:
+    import numpy as np
+    import torch
+    from ccinfer_b200 import kernels
+    from ccinfer_b200.config import Qwen3Config
+    from ccinfer_b200.engine.engine import Engine, EngineOptions, StepEntry
+
+    if args.design != "tugelorn":
+        print(json.dumps({"error": f"unknown design {args.design!r}"}))
+        return 2
+    peaks = load_peaks()
+    layers = args.layers or 6
+    chunk, ctx, page = 2048, 2048, 16
+    rng = np.random.RandomState(0)
+
+    def engine(cfg, graphs):
+        return Engine.from_random(cfg, 42, options=EngineOptions(
+            dtype="bfloat16", kv_tokens=10 * (ctx + 256) + 8192 + 64, max_requests=9, max_tokens_per_step=chunk,
+            max_context=8192 + 64, use_graphs=graphs, use_pdl=args.pdl))
+
+    def timed(fn, reps):
+        ms = []
+        for _ in range(reps):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ms.append(a.elapsed_time(b))
+        return statistics.median(ms)
+
+    def prefill(eng, V, T):
+        toks = rng.randint(0, V, size=T).tolist()
+
+        def once():
+            eng.open_request("p")
+            for i in range(0, T, chunk):
+                eng.step([StepEntry("p", toks[i:i + chunk], [len(toks[i:i + chunk]) - 1] if i + chunk >= T else [])])
+            eng.close_request("p")
+        for _ in range(3):
+            once()
+        return T / (timed(once, 5) * 1e-3)
+
+    def decode(eng, V, B, steps):
+        for b in range(B):
+            eng.open_request(b)
+            eng.step([StepEntry(b, rng.randint(0, V, size=ctx).tolist(), [])])
+        for _ in range(max(3, args.warmup)):
+            eng.step([StepEntry(b, [7], [0]) for b in range(B)])
+        l0 = kernels.counters.own + kernels.counters.library
+        ms = timed(lambda: [eng.step([StepEntry(b, [9], [0]) for b in range(B)]) for _ in range(steps)], 3)
+        launches = (kernels.counters.own + kernels.counters.library - l0) // (3 * steps)
+        for b in range(B):
+            eng.close_request(b)
+        return B * steps / (ms * 1e-3), ms / steps, launches
+
+    if args.design_profile:
+        cfg = tugelorn_config(args.design_sizes.split(",")[0], layers)
+        eng = engine(cfg, False)
+        eng.open_request("p")
+        eng.step([StepEntry("p", rng.randint(0, cfg.vocab, size=chunk).tolist(), [chunk - 1])])
+        for s in range(4):
+            eng.step([StepEntry("p", [5 + s], [0])])
+        torch.cuda.synchronize()
+        eng.check()
+        print("[bench] design profile steps done", file=sys.stderr)
+        return 0
+
+    for size in [x for x in args.design_sizes.split(",") if x]:
+        D, H, G, hd, F, V = DESIGN_SIZES[size]
+        qwen = Qwen3Config.from_json(dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=D, num_attention_heads=H,
+                                          num_key_value_heads=G, head_dim=hd, intermediate_size=F, vocab_size=V))
+        out = {"design": "tugelorn", "beside": "qwen3", "size": size, "layers": layers, "width": D, "q_heads": H,
+               "kv_heads": G, "head_dim": hd, "intermediate": F, "vocab": V, "dtype": "bf16",
+               "data": "synthetic (random weights, random token ids)", "peaks": peaks.get("source", "measured"),
+               "l2": "every step reads all weights, more than the 126 MB L2"}
+        for name, cfg in (("tugelorn", tugelorn_config(size, layers)), ("qwen3", qwen)):
+            sampler = ClockSampler()
+            sampler.start()
+            eng = engine(cfg, True)
+            r = {"prefill_2048_tok_s": round(prefill(eng, V, 2048)), "prefill_8192_tok_s": round(prefill(eng, V, 8192))}
+            for B in (1, 8):
+                tok_s, ms, launches = decode(eng, V, B, max(8, args.steps))
+                r[f"decode_b{B}_tok_s"] = round(tok_s, 1)
+                r[f"decode_b{B}_ms_per_step"] = round(ms, 4)
+                r[f"decode_b{B}_launches_per_step"] = int(launches)
+            eng.check()
+            sampler.stop()
+            r["clocks"] = sampler.summary()
+            out[name] = r
+            del eng
+            torch.cuda.empty_cache()
+        out["ratio"] = {k: round(out["tugelorn"][k] / out["qwen3"][k], 3) for k in out["qwen3"] if k.endswith("tok_s")}
+        print(json.dumps(out), flush=True)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -282,6 +415,9 @@ def main() -> int:
     ap.add_argument("--shape", default="8b", choices=["8b", "14b", "32b"], help="layer shape of --profile-steps")
     ap.add_argument("--workload", default="decode", choices=["decode", "mix14b", "long32b"],
                     help="decode (the default line) or one of the two other workloads of the benchmark record")
+    ap.add_argument("--design", default=None, help="tugelorn: that design beside Qwen3 at equal layer sizes")
+    ap.add_argument("--design-sizes", default="mid,8b", help="layer sizes of --design: " + ", ".join(DESIGN_SIZES))
+    ap.add_argument("--design-profile", action="store_true", help="with --design: a prompt and four eager decode steps")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -295,6 +431,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design:
+        return run_design(args)
     if args.profile_steps:
         return run_profile_steps(args)
     if args.workload != "decode":

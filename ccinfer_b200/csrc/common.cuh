@@ -99,6 +99,22 @@ __device__ __forceinline__ float row_ssq(const float* row, int n, int lane) {
   return ss;
 }
 
+// The gated activation of a feed-forward, as the epilogue of its gate|up product:
+//   limit <= 0:  silu(g) * u
+//   limit  > 0:  g' = min(g, limit), u' = clamp(u, -limit, limit);  g' * sigmoid(alpha g') * (u' + shift)
+struct CcbGluAct {
+  float limit, alpha, shift;
+};
+
+__device__ __forceinline__ float glu_act(const CcbGluAct a, float g, float u) {
+  if (a.limit > 0.f) {
+    g = fminf(g, a.limit);
+    u = fminf(fmaxf(u, -a.limit), a.limit);
+    return g / (1.f + __expf(-a.alpha * g)) * (u + a.shift);
+  }
+  return g / (1.f + __expf(-g)) * u;
+}
+
 __device__ __forceinline__ void set_status(int* status, int bit) {
   if (status != nullptr) atomicOr(status, bit);
 }

@@ -9,11 +9,10 @@
 // Four kernels:
 //   delta_prepare       one block per token: convolution + silu, unit norms, beta, decay -> float rows
 //   conv_state_update   the last (taps - 1) projection rows of each request -> its convolution state
-//   delta_recurrence    one block per (request, head, 32 value channels): walks the step's tokens of the
+//   delta_recurrence    one block per (request, head, 16 value channels): walks the step's tokens of the
 //                       request in order; a column of S is independent of the others, so each is held by
-//                       8 lanes (rows r = 8 i + lane) in registers and two 8-lane sums per token give
-//                       S^T k and S^T q.  The rows of q, k, g of the next 16 tokens are fetched with
-//                       cp.async while the current ones are used.
+//                       8 lanes in registers and 8-lane sums per token give S^T k and S^T q.  The rows of
+//                       q, k, g of the next 16 tokens are fetched with cp.async while the current ones are used.
 //   gated_head_rmsnorm  o / rms(o) * w * sigmoid(gate) per head -> the compute type
 //
 // State of a request (slot s): S as [heads, value channels, key channels] floats (a column of S is
@@ -129,7 +128,7 @@ __global__ void conv_state_update_kernel(const T* __restrict__ proj, int ld, int
 
 // ---------------------------------------------------------------------------------------------
 constexpr int kLanes = 8;          // lanes that share a column of S
-constexpr int kCols = 32;          // columns of S per block
+constexpr int kCols = 16;          // columns of S per block
 constexpr int kRecThreads = kLanes * kCols;
 
 __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
@@ -139,7 +138,38 @@ __device__ __forceinline__ void cp_async4(float* smem, const float* gmem) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 
-// R: rows of S per lane (key channels padded to 8 R).  TCH tokens are staged at a time.
+// Rows of a column that lane `lane` holds: in runs of V = min(R, 4) neighbours (one 16-byte access of
+// shared memory per run where V = 4), the lanes' runs side by side: row(i) = (i / V) * 8 V + lane V + i % V.
+template <int R>
+struct Rows {
+  static constexpr int V = R < 4 ? R : 4;
+  static __device__ __forceinline__ int row(int i, int lane) { return (i / V) * (kLanes * V) + lane * V + (i % V); }
+  static __device__ __forceinline__ void load(const float* base, int lane, float* out) {
+    if constexpr (V == 4) {
+#pragma unroll
+      for (int j = 0; j < R / 4; ++j) {
+        const float4 x = *reinterpret_cast<const float4*>(base + j * (kLanes * 4) + lane * 4);
+        out[4 * j] = x.x; out[4 * j + 1] = x.y; out[4 * j + 2] = x.z; out[4 * j + 3] = x.w;
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < R; ++i) out[i] = base[row(i, lane)];
+    }
+  }
+};
+
+__device__ __forceinline__ float lanes_sum(float v) {
+#pragma unroll
+  for (int o = kLanes / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+// R: rows of S per lane (key channels padded to 8 R).  `tch` tokens are staged at a time.
+//
+// What one token costs is the chain S -> S^T k -> u -> S.  So S^T k and S^T q are both taken from the decayed
+// state before the write (o = (gS)^T q + u (k . q), which is the read-out after the write), their sums over
+// the lanes run side by side, each sum over a lane's rows is four shorter chains, and the read-out is off the
+// chain altogether.
 template <int R>
 __global__ void __launch_bounds__(kRecThreads)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
@@ -148,7 +178,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
                         int G, int H, int dk, int dv, int tch) {
   ccb::pdl_begin();
   constexpr int DP = R * kLanes;
-  extern __shared__ float smem[];
+  extern __shared__ __align__(16) float smem[];
   const int e = blockIdx.z, head = blockIdx.y;
   const int slot = state_slot[e];
   if (slot < 0) return;
@@ -159,8 +189,8 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   const int cl = threadIdx.x / kLanes;
   const int col = blockIdx.x * kCols + cl;
   const bool live = col < dv;
-  // a stage: q, k, g rows [tch][DP] each, then v [tch][kCols], then beta [tch]
-  const int stage_floats = tch * (3 * DP + kCols + 1);
+  // a stage: q, k, g rows [tch][DP] each, then v [tch][kCols], then beta [tch] (padded to a multiple of 4)
+  const int stage_floats = tch * (3 * DP + kCols) + ((tch + 3) & ~3);
   auto sq = [&](int s) { return smem + (size_t)s * stage_floats; };
 
   // rows past dk never change: q = k = 0, g = 1 there (the loads never touch them)
@@ -201,7 +231,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   float* sp = state + (((size_t)slot * H + head) * dv + (live ? col : 0)) * dk;
 #pragma unroll
   for (int i = 0; i < R; ++i) {
-    const int r = i * kLanes + lane;
+    const int r = Rows<R>::row(i, lane);
     S[i] = (live && r < dk) ? sp[r] : 0.f;
   }
 
@@ -215,36 +245,40 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
     const float* sv = base + 3 * tch * DP;
     const float* sb = sv + tch * kCols;
     const int cnt = min(tch, n - c * tch);
+#pragma unroll 2
     for (int tt = 0; tt < cnt; ++tt) {
-      const float* q = base + tt * DP;
-      const float* k = base + tch * DP + tt * DP;
-      const float* g = base + 2 * tch * DP + tt * DP;
-      float kr[R];
-      float dot = 0.f;
+      float qr[R], kr[R], gr[R];
+      Rows<R>::load(base + tt * DP, lane, qr);
+      Rows<R>::load(base + tch * DP + tt * DP, lane, kr);
+      Rows<R>::load(base + 2 * tch * DP + tt * DP, lane, gr);
+      const float beta = sb[tt], v = sv[tt * kCols + cl];
+      constexpr int P = R < 4 ? R : 4;   // partial sums per lane
+      float dkp[P], dqp[P], kqp[P];
+#pragma unroll
+      for (int p = 0; p < P; ++p) dkp[p] = dqp[p] = kqp[p] = 0.f;
 #pragma unroll
       for (int i = 0; i < R; ++i) {
-        kr[i] = k[i * kLanes + lane];
-        S[i] *= g[i * kLanes + lane];
-        dot = fmaf(S[i], kr[i], dot);
+        S[i] *= gr[i];
+        dkp[i % P] = fmaf(S[i], kr[i], dkp[i % P]);
+        dqp[i % P] = fmaf(S[i], qr[i], dqp[i % P]);
+        kqp[i % P] = fmaf(kr[i], qr[i], kqp[i % P]);
       }
+      float dkk = dkp[0], dqq = dqp[0], kq = kqp[0];
 #pragma unroll
-      for (int o = kLanes / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = sb[tt] * (sv[tt * kCols + cl] - dot);
-      float od = 0.f;
+      for (int p = 1; p < P; ++p) dkk += dkp[p], dqq += dqp[p], kq += kqp[p];
+      dkk = lanes_sum(dkk);
+      dqq = lanes_sum(dqq);
+      kq = lanes_sum(kq);
+      const float u = beta * (v - dkk);
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        S[i] = fmaf(kr[i], u, S[i]);
-        od = fmaf(S[i], q[i * kLanes + lane], od);
-      }
-#pragma unroll
-      for (int o = kLanes / 2; o > 0; o >>= 1) od += __shfl_xor_sync(0xffffffffu, od, o);
-      if (live && lane == 0) out[((size_t)(r0 + c * tch + tt) * H + head) * dv + col] = od;
+      for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], u, S[i]);
+      if (live && lane == 0) out[((size_t)(r0 + c * tch + tt) * H + head) * dv + col] = fmaf(u, kq, dqq);
     }
   }
   if (live) {
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-      const int r = i * kLanes + lane;
+      const int r = Rows<R>::row(i, lane);
       if (r < dk) sp[r] = S[i];
     }
   }
@@ -319,7 +353,7 @@ CCB_API int ccb_delta_recurrence(const float* qn, const float* kn, const float* 
   while (R * kLanes < dk) R *= 2;
   const int DP = R * kLanes;
   const int tch = DP <= 128 ? 16 : 8;
-  const size_t smem = (size_t)2 * tch * (3 * DP + kCols + 1) * sizeof(float);
+  const size_t smem = (size_t)2 * (tch * (3 * DP + kCols) + ((tch + 3) & ~3)) * sizeof(float);
   dim3 grid((dv + kCols - 1) / kCols, H, n_entries);
 #define CCB_REC(RR)                                                                                              \
   cudaFuncSetAttribute(delta_recurrence_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \

@@ -168,6 +168,31 @@ __global__ void clamped_glu_kernel(T* __restrict__ act, const T* __restrict__ gu
   }
 }
 
+// bf16, F and the block multiples of 8: eight elements (16 bytes) per thread and access
+__global__ void clamped_glu_bf16x8_kernel(uint4* __restrict__ act, const uint4* __restrict__ gu, int F8, int B8,
+                                          size_t total8, const CcbGluAct a) {
+  ccb::pdl_begin();
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)gridDim.x * blockDim.x;
+  for (; i < total8; i += stride) {
+    const size_t t = i / F8;
+    const int f = (int)(i - t * F8);
+    const uint4* row = gu + t * 2 * (size_t)F8;
+    const int gi = (f / B8) * 2 * B8 + f % B8;
+    const uint4 g = row[gi], u = row[gi + B8];
+    const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* uh = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = __bfloat1622float2(gh[e]), y = __bfloat1622float2(uh[e]);
+      oh[e] = __floats2bfloat162_rn(glu_act(a, x.x, y.x), glu_act(a, x.y, y.y));
+    }
+    act[i] = o;
+  }
+}
+
 CCB_API int ccb_clamped_glu(void* act, const void* gate_up, int T_, int F, int block, float limit, float alpha,
                             float up_shift, int dtype, cudaStream_t stream) {
   if (T_ <= 0) return 0;
@@ -175,6 +200,14 @@ CCB_API int ccb_clamped_glu(void* act, const void* gate_up, int T_, int F, int b
   const int B = block == 0 ? F : block;
   const size_t total = (size_t)T_ * F;
   const int threads = 256;
+  if (dtype == CCB_BF16 && limit > 0.f && (F % 8) == 0 && (B % 8) == 0 &&
+      ((reinterpret_cast<uintptr_t>(act) | reinterpret_cast<uintptr_t>(gate_up)) & 15) == 0) {
+    const size_t total8 = total / 8;
+    const size_t want = (total8 + threads - 1) / threads;
+    ccb_launch(clamped_glu_bf16x8_kernel, (int)(want < 148 * 32 ? want : 148 * 32), threads, 0, stream, (uint4*)act,
+               (const uint4*)gate_up, F / 8, B / 8, total8, CcbGluAct{limit, alpha, up_shift});
+    return ccb_launch_status();
+  }
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
   if (dtype == CCB_F32)
     ccb_launch(clamped_glu_kernel<float>, blocks, threads, 0, stream, (float*)act, (const float*)gate_up, F, B, total,

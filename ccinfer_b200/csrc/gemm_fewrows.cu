@@ -58,7 +58,6 @@ __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   return r;
 }
 
-__device__ __forceinline__ float silu_fr(float g) { return g / (1.f + __expf(-g)); }
 
 }  // namespace
 
@@ -80,7 +79,8 @@ namespace {
 template <int NB, int STAGES, typename TOut>
 __global__ void __launch_bounds__(FR_THREADS)
 gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
-                    TOut* __restrict__ C, int M, int N, int K, int ldc, int swiglu, const CcbNormFuse fuse, int* status) {
+                    TOut* __restrict__ C, int M, int N, int K, int ldc, int swiglu, const CcbGluAct act,
+                    const CcbNormFuse fuse, int* status) {
   __shared__ float s_scale[16];
   constexpr int X_BYTES = 8 * NB * FR_KC * 2;
   constexpr int RED_LD = 8 * NB + 1;
@@ -234,7 +234,7 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
             u += red[(w * 16 + f + 8) * RED_LD + tok];
           }
           if (scaled) g *= s_scale[tok], u *= s_scale[tok];
-          C[(size_t)tok * ldc + ch0 + f] = from_f32<TOut>(silu_fr(g) * u);
+          C[(size_t)tok * ldc + ch0 + f] = from_f32<TOut>(glu_act(act, g, u));
         }
       }
     } else {
@@ -254,6 +254,9 @@ gemm_fewrows_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
 int g_fr_stages = 0;  // 0: the default of the shape
 
+// the activation of the call in progress: set by the entry point, read where the kernel is launched
+static thread_local CcbGluAct t_glu_act = {0.f, 1.f, 0.f};
+
 template <int NB, int STAGES, typename TOut>
 int launch_fewrows(const CUtensorMap& tmW, const CUtensorMap& tmX, void* C, int M, int N, int K, int ldc, int swiglu,
                    const CcbNormFuse& fuse, int* status, cudaStream_t stream) {
@@ -268,7 +271,7 @@ int launch_fewrows(const CUtensorMap& tmW, const CUtensorMap& tmX, void* C, int 
   }
   const int blocks = swiglu ? (N / 2 + 7) / 8 : (N + FR_ROWS - 1) / FR_ROWS;
   ccb_launch_ex(true, gemm_fewrows_kernel<NB, STAGES, TOut>, dim3(blocks), FR_THREADS, smem, stream, tmW, tmX,
-                (TOut*)C, M, N, K, ldc, swiglu, fuse, status);
+                (TOut*)C, M, N, K, ldc, swiglu, t_glu_act, fuse, status);
   return ccb_launch_status();
 }
 
@@ -341,6 +344,17 @@ static int fewrows_checked(void* C, const void* A, const void* W, int M, int N, 
 CCB_API int ccb_gemm_fewrows_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
                                   int ldc, int out_dtype, int swiglu, int* status, cudaStream_t stream) {
   return fewrows_checked(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, swiglu, CcbNormFuse{}, status, stream);
+}
+
+// The gated form with the clamped activation of ccb::glu_act in place of silu(gate) * up (limit > 0).
+CCB_API int ccb_gemm_fewrows_glu_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                                      int ldc, int out_dtype, float limit, float alpha, float shift, int* status,
+                                      cudaStream_t stream) {
+  if (!(limit > 0.f)) return CCB_REFUSE_ARG;
+  t_glu_act = CcbGluAct{limit, alpha, shift};
+  const int rc = fewrows_checked(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, 1, CcbNormFuse{}, status, stream);
+  t_glu_act = CcbGluAct{0.f, 1.f, 0.f};
+  return rc;
 }
 
 // Number of blocks of the plain product, which is the number of partial sums that the "into the residual

@@ -135,7 +135,8 @@ __device__ __forceinline__ void pstore16<__nv_bfloat16>(__nv_bfloat16* dst, cons
 template <bool SWIGLU, typename TOut>
 __global__ void __launch_bounds__(kPairGemmThreads, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                    TOut* __restrict__ C, int ldc, int rowsA, int rowsB, int K, int* status) {
+                    TOut* __restrict__ C, int ldc, int rowsA, int rowsB, int K, const ccb::CcbGluAct act,
+                    int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* sA = smem;
@@ -273,7 +274,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const float gv = __uint_as_float(g[j]);
-              g[j] = __float_as_uint(gv / (1.f + __expf(-gv)) * __uint_as_float(u[j]));
+              g[j] = __float_as_uint(ccb::glu_act(act, gv, __uint_as_float(u[j])));
             }
             if (ga < rowsA) {
 #pragma unroll
@@ -302,6 +303,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 }
 
+// the activation of the call in progress: set by the entry point, read where the kernel is launched
+static thread_local ccb::CcbGluAct t_glu_act = {0.f, 1.f, 0.f};
+
 template <bool SWIGLU, typename TOut>
 int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, int M, int N, int K, int sms, int* status,
                 cudaStream_t stream) {
@@ -328,7 +332,7 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU, TOut>, tmA, tmB, (TOut*)C, ldc, M, N, K, status);
+  cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<SWIGLU, TOut>, tmA, tmB, (TOut*)C, ldc, M, N, K, t_glu_act, status);
   return ccb_launch_status();
 }
 
@@ -337,8 +341,28 @@ int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc
 // C[M, N] = A[M, K] W[N, K]^T (bfloat16 operands, bfloat16 or float result), a pair of SMs per 256 x 256 tile.
 // swiglu: W [N = 2F, K] in blocks of 64 gate and 64 up rows (F a multiple of 64), C [M, F] = silu(gate) * up.
 // K and the row strides are multiples of 8 elements, the bases 16-byte aligned.
+static int tc_pair(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
+                   int out_dtype, int swiglu, int sms, int* status, cudaStream_t stream);
+
 CCB_API int ccb_gemm_tc_pair_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
                                   int out_dtype, int swiglu, int sms, int* status, cudaStream_t stream) {
+  t_glu_act = ccb::CcbGluAct{0.f, 1.f, 0.f};
+  return tc_pair(C, A, W, M, N, K, lda, ldw, ldc, out_dtype, swiglu, sms, status, stream);
+}
+
+// The gated form with the clamped activation of ccb::glu_act in place of silu(gate) * up (limit > 0).
+CCB_API int ccb_gemm_tc_pair_glu_bf16(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw,
+                                      int ldc, float limit, float alpha, float shift, int sms, int* status,
+                                      cudaStream_t stream) {
+  if (!(limit > 0.f)) return CCB_REFUSE_ARG;
+  t_glu_act = ccb::CcbGluAct{limit, alpha, shift};
+  const int rc = tc_pair(C, A, W, M, N, K, lda, ldw, ldc, CCB_BF16, 1, sms, status, stream);
+  t_glu_act = ccb::CcbGluAct{0.f, 1.f, 0.f};
+  return rc;
+}
+
+static int tc_pair(void* C, const void* A, const void* W, int M, int N, int K, int lda, int ldw, int ldc,
+                   int out_dtype, int swiglu, int sms, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (out_dtype != CCB_F32 && out_dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
   if (K <= 0 || (K & 7) || lda < K || ldw < K || ldc < (swiglu ? N / 2 : N) || (lda & 7) || (ldw & 7) || sms < 2 ||

@@ -86,7 +86,7 @@ template <int BN, int STAGES, bool SWAP, typename TOut>
 __global__ void __launch_bounds__(kThreadsTc, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, TOut* __restrict__ C,
                int ldc, int rowsA, int rowsB, int K, int splits, float* __restrict__ partial,
-               int* __restrict__ counters, int swiglu, const CcbRowScale rs, int* status) {
+               int* __restrict__ counters, int swiglu, const CcbGluAct act, const CcbRowScale rs, int* status) {
   __shared__ float s_scale[16];
   constexpr int B_STAGE_BYTES = BN * BK * 2;
   constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
@@ -223,7 +223,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (j < rowsB) {
               float g = __uint_as_float(v[j]), u = xch[row * 17 + j];
               if (scaled) g *= s_scale[j], u *= s_scale[j];
-              C[(size_t)j * ldc + ch] = from_f32<TOut>(g / (1.f + __expf(-g)) * u);
+              C[(size_t)j * ldc + ch] = from_f32<TOut>(glu_act(act, g, u));
             }
           }
         }
@@ -392,6 +392,9 @@ bool tensor_map(const void* ptr, int rows, int K, int ld, int box_rows, CUtensor
   return ccb_tensor_map_2d(ptr, rows, K, ld, BK, box_rows, out);
 }
 
+// the activation of the call in progress: set by the entry point, read where the kernel is launched
+static thread_local CcbGluAct t_glu_act = {0.f, 1.f, 0.f};
+
 template <int BN, int STAGES, bool SWAP, typename TOut>
 int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, int rowsA, int rowsB, int K,
               int splits, float* partial, int* counters, int* status, cudaStream_t stream, int swiglu = 0,
@@ -406,7 +409,7 @@ int launch_tc(const CUtensorMap& tmA, const CUtensorMap& tmB, void* C, int ldc, 
   }
   dim3 grid((rowsA + BM - 1) / BM, (rowsB + BN - 1) / BN, splits);
   ccb_launch_ex(true, gemm_tc_kernel<BN, STAGES, SWAP, TOut>, grid, kThreadsTc, smem, stream, 
-      tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, swiglu, rs, status);
+      tmA, tmB, (TOut*)C, ldc, rowsA, rowsB, K, splits, partial, counters, swiglu, t_glu_act, rs, status);
   return ccb_launch_status();
 }
 
@@ -472,6 +475,16 @@ static int tc_swiglu(void* act, const void* A, const void* W, int M, int F, int 
 CCB_API int ccb_gemm_tc_swiglu_bf16(void* act, const void* A, const void* W, int M, int F, int K, int lda, int ldw,
                                     int ld_act, int* status, cudaStream_t stream) {
   return tc_swiglu(act, A, W, M, F, K, lda, ldw, ld_act, CcbRowScale{}, status, stream);
+}
+
+// The same with the clamped activation of ccb::glu_act in place of silu(gate) * up (limit > 0).
+CCB_API int ccb_gemm_tc_glu_bf16(void* act, const void* A, const void* W, int M, int F, int K, int lda, int ldw,
+                                 int ld_act, float limit, float alpha, float shift, int* status, cudaStream_t stream) {
+  if (!(limit > 0.f)) return CCB_REFUSE_ARG;
+  t_glu_act = CcbGluAct{limit, alpha, shift};
+  const int rc = tc_swiglu(act, A, W, M, F, K, lda, ldw, ld_act, CcbRowScale{}, status, stream);
+  t_glu_act = CcbGluAct{0.f, 1.f, 0.f};
+  return rc;
 }
 
 // The same with the factor of a norm for every token (see CcbRowScale).

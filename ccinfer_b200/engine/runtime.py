@@ -144,15 +144,30 @@ class Runtime:
 
         A few tokens in bfloat16 with the blocked layout: one kernel (the activation is the product's
         epilogue).  Otherwise the product into scratch and the activation kernel.
-        ``activation`` ("clamped_glu", limit, alpha, shift): that activation in place of silu(g) * u; the
-        product's epilogues know silu only, so it is always a kernel of its own."""
+        ``activation`` ("clamped_glu", limit, alpha, shift): that activation in place of silu(g) * u, in the
+        same epilogues or as a kernel of its own."""
         if activation is not None:
-            x = self.rows(x)
-            gu = self.scratch.get("ffn_gate_up", (self.max_tokens, w.shape[0]), self.dtype)[:x.shape[0]]
-            self.linear(gu, x, w)
             kind, limit, alpha, shift = activation
             if kind != "clamped_glu":
                 raise Unsupported(f"gated activation {kind!r}")
+            x = self.rows(x)
+            M, K = x.shape
+            N = w.shape[0]
+            blocked = self.dtype == torch.bfloat16 and block == kernels.SWIGLU_BLOCK
+            fused = None   # the same choice of product as for silu(g) * u below, the activation in its epilogue
+            if (blocked and M <= kernels.SKINNY_MAX_ROWS and kernels.gemm_tc_fits(K, x, w)
+                    and -(-N // 128) >= self.sm_count and kernels.gemm_tc_splits(M, N, K) == 1):
+                fused = "tc"
+            elif (blocked and M <= kernels.FEWROWS_MAX_ROWS and K >= kernels.FEWROWS_MIN_K and N % 128 == 0
+                    and kernels.gemm_fewrows_fits(M, K, x, w) and -(-N // 128) < self.sm_count):
+                fused = "fewrows"
+            elif (blocked and M >= kernels.PAIR_SWIGLU_MIN_ROWS and N % 128 == 0 and kernels.gemm_tc_fits(K, x, w)):
+                fused = "pair"
+            if fused is not None:
+                kernels.gemm_glu_bf16(act, x, w, limit, alpha, shift, fused, status=self.status)
+                return act
+            gu = self.scratch.get("ffn_gate_up", (self.max_tokens, N), self.dtype)[:M]
+            self.linear(gu, x, w)
             kernels.clamped_glu(act, gu, block, limit, alpha, shift)
             return act
         un = x if isinstance(x, UnscaledRows) else None

@@ -38,6 +38,12 @@ _SIGNATURES = {
     "ccb_silu_mul": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_gemm_tc_swiglu_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                 c_void_p],
+    "ccb_gemm_tc_glu_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                             c_float, c_void_p, c_void_p],
+    "ccb_gemm_fewrows_glu_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                  c_float, c_float, c_float, c_void_p, c_void_p],
+    "ccb_gemm_tc_pair_glu_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                                  c_float, c_float, c_int, c_void_p, c_void_p],
     "ccb_gemm_fewrows_set_stages": [c_int],
     "ccb_gemm_fewrows_bf16": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_void_p, c_void_p],
@@ -247,6 +253,29 @@ def gemm_tc_swiglu_bf16(act, a, w, status=None) -> None:
     assert w.shape == (2 * F, K) and act.shape == (M, F) and a.stride(1) == w.stride(1) == act.stride(1) == 1
     _check(lib().ccb_gemm_tc_swiglu_bf16(_p(act), _p(a), _p(w), M, F, K, a.stride(0), w.stride(0), act.stride(0),
                                          _p(status), _stream()), "gemm_tc_swiglu_bf16")
+
+
+def gemm_glu_bf16(act, a, w, limit: float, alpha: float, shift: float, kind: str, status=None) -> None:
+    """act[M, F] = glu(a Wg^T, a Wu^T) with the clamped activation of ``clamped_glu`` as the epilogue of the
+    product, w [2F, K] interleaved in blocks of SWIGLU_BLOCK rows.  ``kind``: "tc" (tcgen05, M <= 16),
+    "fewrows" (TMA ring, M <= 16) or "pair" (tcgen05 on pairs of SMs, many rows)."""
+    _cuda(w, status)
+    assert a.dtype == w.dtype == act.dtype == torch.bfloat16 and act.is_cuda and a.is_cuda
+    M, K = a.shape
+    F = act.shape[1]
+    assert w.shape == (2 * F, K) and act.shape[0] == M and F % SWIGLU_BLOCK == 0
+    assert a.stride(1) == 1 and w.stride(1) == 1 and act.stride(1) == 1
+    args = (float(limit), float(alpha), float(shift))
+    if kind == "tc":
+        rc = lib().ccb_gemm_tc_glu_bf16(_p(act), _p(a), _p(w), M, F, K, a.stride(0), w.stride(0), act.stride(0),
+                                        *args, _p(status), _stream())
+    elif kind == "fewrows":
+        rc = lib().ccb_gemm_fewrows_glu_bf16(_p(act), _p(a), _p(w), M, 2 * F, K, a.stride(0), w.stride(0),
+                                             act.stride(0), _dt(act), *args, _p(status), _stream())
+    else:
+        rc = lib().ccb_gemm_tc_pair_glu_bf16(_p(act), _p(a), _p(w), M, 2 * F, K, a.stride(0), w.stride(0),
+                                             act.stride(0), *args, sm_count(), _p(status), _stream())
+    _check(rc, "gemm_glu_bf16")
 
 
 def gemm_tc_swiglu_scaled_bf16(act, a, w, ssq, parts: int, dim: int, eps: float, status=None) -> None:

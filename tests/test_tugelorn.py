@@ -149,6 +149,22 @@ def test_clamped_glu_kernel(dtype, F, block):
 
 
 @gpu
+@pytest.mark.parametrize("kind,M,F,K", [("tc", 1, 9600, 256), ("tc", 16, 9600, 64), ("fewrows", 3, 256, 512),
+                                        ("fewrows", 16, 128, 2048), ("pair", 300, 256, 256), ("pair", 1100, 192, 512)])
+def test_clamped_glu_as_the_epilogue_of_the_product(kind, M, F, K):
+    from ccinfer_b200 import kernels
+    g = torch.Generator().manual_seed(M + F)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(F, K, generator=g) * 2.0 / K ** 0.5).to(torch.bfloat16)
+    wu = (torch.randn(F, K, generator=g) * 2.0 / K ** 0.5).to(torch.bfloat16)
+    w = kernels.interleave_gate_up(wg.cuda(), wu.cuda(), kernels.SWIGLU_BLOCK)
+    act = torch.empty(M, F, dtype=torch.bfloat16, device="cuda")
+    kernels.gemm_glu_bf16(act, x.cuda(), w, 1.5, 1.702, 1.0, kind)
+    want = plain.clamped_glu(x.double() @ wg.double().T, x.double() @ wu.double().T, 1.5)
+    assert (act.cpu().double() - want).abs().max() < 2e-2 * max(1.0, want.abs().max())
+
+
+@gpu
 @pytest.mark.parametrize("H,G,dk,dv", [(2, 1, 8, 8), (3, 3, 24, 40), (4, 2, 64, 70), (2, 2, 130, 33), (1, 1, 256, 16)])
 def test_delta_recurrence_kernel_carries_its_state(H, G, dk, dv):
     """Two requests in unequal portions over three launches, slots 2 and 0 of a state of three."""
