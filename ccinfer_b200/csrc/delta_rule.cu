@@ -7,7 +7,8 @@
 // g = exp(-exp(A_h) softplus(a + dt_bias)).  Everything after the projections is float.
 //
 // Four kernels:
-//   delta_prepare       one block per token: convolution + silu, unit norms, beta, decay -> float rows
+//   delta_prepare       a warp per (token, head of q / k / v / decay): convolution + silu, unit norms, beta,
+//                       decay -> float rows
 //   conv_state_update   the last (taps - 1) projection rows of each request -> its convolution state
 //   delta_recurrence    one block per (request, head, 16 value channels): walks the step's tokens of the
 //                       request in order; a column of S is independent of the others, so each is held by
@@ -31,8 +32,10 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 // proj [T, ld]: columns q (at oq, G*dk), k (at ok, G*dk), v (at ov, H*dv), b (at ob, H); a [T, lda]: H*dk
 // decay pre-activations.  conv_w float [C, taps] for the channels q|k|v in this order (C = 2 G dk + H dv);
 // conv_state [slots, taps-1, C].
+constexpr int kPrepWarps = 4;
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kPrepWarps * 32)
 delta_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov, int ob, const T* __restrict__ a,
                      int lda, const float* __restrict__ conv_w, int taps, const T* __restrict__ conv_state,
                      const float* __restrict__ A_log, const float* __restrict__ dt_bias,
@@ -49,7 +52,7 @@ delta_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov,
   const int lt = t - cu_q[e];  // index of the token within the step's portion of its request
   const int C = 2 * G * dk + H * dv;
   const T* st = conv_state + (size_t)slot * (taps - 1) * C;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
 
   // convolution + silu of channel c (in the order q | k | v), input column `col` of proj
   auto conv = [&](int c, int col) -> float {
@@ -68,7 +71,8 @@ delta_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov,
 
   // units: G query heads, G key heads (unit vectors), H value heads, H decay rows
   const int units = 2 * G + 2 * H;
-  for (int u = warp; u < units; u += n_warps) {
+  const int u = blockIdx.y * kPrepWarps + (threadIdx.x >> 5);   // a warp per unit
+  if (u < units) {
     if (u < 2 * G) {
       const bool is_q = u < G;
       const int head = is_q ? u : u - G;
@@ -164,13 +168,14 @@ __device__ __forceinline__ float lanes_sum(float v) {
   return v;
 }
 
-// R: rows of S per lane (key channels padded to 8 R).  `tch` tokens are staged at a time.
+// R: rows of S per lane (key channels padded to 8 R); C: columns of S per thread, which share the rows of q, k
+// and g that the thread has read.  `tch` tokens are staged at a time.
 //
 // What one token costs is the chain S -> S^T k -> u -> S.  So S^T k and S^T q are both taken from the decayed
 // state before the write (o = (gS)^T q + u (k . q), which is the read-out after the write), their sums over
 // the lanes run side by side, each sum over a lane's rows is four shorter chains, and the read-out is off the
 // chain altogether.
-template <int R>
+template <int R, int C>
 __global__ void __launch_bounds__(kRecThreads)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
                         const float* __restrict__ gg, const float* __restrict__ bb, float* __restrict__ state,
@@ -178,6 +183,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
                         int G, int H, int dk, int dv, int tch) {
   ccb::pdl_begin();
   constexpr int DP = R * kLanes;
+  constexpr int COLS = kCols * C;   // columns of S per block
   extern __shared__ __align__(16) float smem[];
   const int e = blockIdx.z, head = blockIdx.y;
   const int slot = state_slot[e];
@@ -187,10 +193,9 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
   const int kvh = head / (H / G);
   const int lane = threadIdx.x & (kLanes - 1);
   const int cl = threadIdx.x / kLanes;
-  const int col = blockIdx.x * kCols + cl;
-  const bool live = col < dv;
-  // a stage: q, k, g rows [tch][DP] each, then v [tch][kCols], then beta [tch] (padded to a multiple of 4)
-  const int stage_floats = tch * (3 * DP + kCols) + ((tch + 3) & ~3);
+  const int col0 = blockIdx.x * COLS + cl * C;   // this thread's columns: col0 .. col0 + C - 1
+  // a stage: q, k, g rows [tch][DP] each, then v [tch][COLS], then beta [tch] (padded to a multiple of 4)
+  const int stage_floats = tch * (3 * DP + COLS) + ((tch + 3) & ~3);
   auto sq = [&](int s) { return smem + (size_t)s * stage_floats; };
 
   // rows past dk never change: q = k = 0, g = 1 there (the loads never touch them)
@@ -217,71 +222,90 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       cp_async4(base + 2 * tch * DP + tt * DP + r, gg + (row * H + head) * dk + r);
     }
     float* sv = base + 3 * tch * DP;
-    for (int i = threadIdx.x; i < cnt * kCols; i += kRecThreads) {
-      const int tt = i / kCols, c = i - tt * kCols;
-      const int gc = blockIdx.x * kCols + c;
+    for (int i = threadIdx.x; i < cnt * COLS; i += kRecThreads) {
+      const int tt = i / COLS, c = i - tt * COLS;
+      const int gc = blockIdx.x * COLS + c;
       if (gc < dv) cp_async4(sv + i, vv + ((size_t)(r0 + t0 + tt) * H + head) * dv + gc);
     }
-    float* sb = sv + tch * kCols;
+    float* sb = sv + tch * COLS;
     for (int i = threadIdx.x; i < cnt; i += kRecThreads) cp_async4(sb + i, bb + (size_t)(r0 + t0 + i) * H + head);
     cp_async_commit();
   };
 
-  float S[R];
-  float* sp = state + (((size_t)slot * H + head) * dv + (live ? col : 0)) * dk;
+  float S[C][R];
+  float* sp = state + ((size_t)slot * H + head) * dv * dk;
 #pragma unroll
-  for (int i = 0; i < R; ++i) {
-    const int r = Rows<R>::row(i, lane);
-    S[i] = (live && r < dk) ? sp[r] : 0.f;
-  }
+  for (int c = 0; c < C; ++c)
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+      const int r = Rows<R>::row(i, lane);
+      S[c][i] = (col0 + c < dv && r < dk) ? sp[(size_t)(col0 + c) * dk + r] : 0.f;
+    }
 
   const int chunks = (n + tch - 1) / tch;
   fetch(0, 0);
-  for (int c = 0; c < chunks; ++c) {
+  for (int ch = 0; ch < chunks; ++ch) {
     cp_async_wait_all();
-    __syncthreads();  // chunk c is in stage c & 1; everyone is done with stage (c + 1) & 1
-    if (c + 1 < chunks) fetch(c + 1, (c + 1) & 1);
-    const float* base = sq(c & 1);
+    __syncthreads();  // chunk ch is in stage ch & 1; everyone is done with stage (ch + 1) & 1
+    if (ch + 1 < chunks) fetch(ch + 1, (ch + 1) & 1);
+    const float* base = sq(ch & 1);
     const float* sv = base + 3 * tch * DP;
-    const float* sb = sv + tch * kCols;
-    const int cnt = min(tch, n - c * tch);
+    const float* sb = sv + tch * COLS;
+    const int cnt = min(tch, n - ch * tch);
 #pragma unroll 2
     for (int tt = 0; tt < cnt; ++tt) {
       float qr[R], kr[R], gr[R];
       Rows<R>::load(base + tt * DP, lane, qr);
       Rows<R>::load(base + tch * DP + tt * DP, lane, kr);
       Rows<R>::load(base + 2 * tch * DP + tt * DP, lane, gr);
-      const float beta = sb[tt], v = sv[tt * kCols + cl];
+      const float beta = sb[tt];
       constexpr int P = R < 4 ? R : 4;   // partial sums per lane
-      float dkp[P], dqp[P], kqp[P];
+      float kqp[P];
 #pragma unroll
-      for (int p = 0; p < P; ++p) dkp[p] = dqp[p] = kqp[p] = 0.f;
+      for (int p = 0; p < P; ++p) kqp[p] = 0.f;
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        S[i] *= gr[i];
-        dkp[i % P] = fmaf(S[i], kr[i], dkp[i % P]);
-        dqp[i % P] = fmaf(S[i], qr[i], dqp[i % P]);
-        kqp[i % P] = fmaf(kr[i], qr[i], kqp[i % P]);
+      for (int i = 0; i < R; ++i) kqp[i % P] = fmaf(kr[i], qr[i], kqp[i % P]);
+      float kq = kqp[0];
+#pragma unroll
+      for (int p = 1; p < P; ++p) kq += kqp[p];
+      float dkk[C], dqq[C];
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        float dkp[P], dqp[P];
+#pragma unroll
+        for (int p = 0; p < P; ++p) dkp[p] = dqp[p] = 0.f;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          S[c][i] *= gr[i];
+          dkp[i % P] = fmaf(S[c][i], kr[i], dkp[i % P]);
+          dqp[i % P] = fmaf(S[c][i], qr[i], dqp[i % P]);
+        }
+        dkk[c] = dkp[0], dqq[c] = dqp[0];
+#pragma unroll
+        for (int p = 1; p < P; ++p) dkk[c] += dkp[p], dqq[c] += dqp[p];
       }
-      float dkk = dkp[0], dqq = dqp[0], kq = kqp[0];
 #pragma unroll
-      for (int p = 1; p < P; ++p) dkk += dkp[p], dqq += dqp[p], kq += kqp[p];
-      dkk = lanes_sum(dkk);
-      dqq = lanes_sum(dqq);
+      for (int c = 0; c < C; ++c) dkk[c] = lanes_sum(dkk[c]);
       kq = lanes_sum(kq);
-      const float u = beta * (v - dkk);
 #pragma unroll
-      for (int i = 0; i < R; ++i) S[i] = fmaf(kr[i], u, S[i]);
-      if (live && lane == 0) out[((size_t)(r0 + c * tch + tt) * H + head) * dv + col] = fmaf(u, kq, dqq);
+      for (int c = 0; c < C; ++c) dqq[c] = lanes_sum(dqq[c]);
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        const float u = beta * (sv[tt * COLS + cl * C + c] - dkk[c]);
+#pragma unroll
+        for (int i = 0; i < R; ++i) S[c][i] = fmaf(kr[i], u, S[c][i]);
+        if (lane == c % kLanes && col0 + c < dv)
+          out[((size_t)(r0 + ch * tch + tt) * H + head) * dv + col0 + c] = fmaf(u, kq, dqq[c]);
+      }
     }
   }
-  if (live) {
+#pragma unroll
+  for (int c = 0; c < C; ++c)
 #pragma unroll
     for (int i = 0; i < R; ++i) {
       const int r = Rows<R>::row(i, lane);
-      if (r < dk) sp[r] = S[i];
+      if (col0 + c < dv && r < dk) sp[(size_t)(col0 + c) * dk + r] = S[c][i];
     }
-  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -314,12 +338,13 @@ CCB_API int ccb_delta_prepare(const void* proj, int ld, int oq, int ok, int ov, 
                               cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (G <= 0 || H <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 1) return CCB_REFUSE_SIZE;
+  const dim3 grid(T_, (2 * G + 2 * H + kPrepWarps - 1) / kPrepWarps);
   if (dtype == CCB_F32)
-    ccb_launch(delta_prepare_kernel<float>, dim3(T_), dim3(256), 0, stream, (const float*)proj, ld, oq, ok, ov, ob,
+    ccb_launch(delta_prepare_kernel<float>, grid, dim3(kPrepWarps * 32), 0, stream, (const float*)proj, ld, oq, ok, ov, ob,
                (const float*)a, lda, conv_w, taps, (const float*)conv_state, A_log, dt_bias, entry_of_token, cu_q,
                state_slot, qn, kn, vv, gg, bb, G, H, dk, dv, q_mult, unit_eps);
   else if (dtype == CCB_BF16)
-    ccb_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(T_), dim3(256), 0, stream, (const __nv_bfloat16*)proj, ld,
+    ccb_launch(delta_prepare_kernel<__nv_bfloat16>, grid, dim3(kPrepWarps * 32), 0, stream, (const __nv_bfloat16*)proj, ld,
                oq, ok, ov, ob, (const __nv_bfloat16*)a, lda, conv_w, taps, (const __nv_bfloat16*)conv_state, A_log,
                dt_bias, entry_of_token, cu_q, state_slot, qn, kn, vv, gg, bb, G, H, dk, dv, q_mult, unit_eps);
   else
@@ -344,6 +369,19 @@ CCB_API int ccb_conv_state_update(const void* proj, int ld, int oq, int ok, int 
   return ccb_launch_status();
 }
 
+template <int R, int C>
+static void launch_recurrence(const float* qn, const float* kn, const float* vv, const float* gg, const float* bb,
+                              float* state, float* out, const int* cu_q, const int* state_slot, int n_entries, int G,
+                              int H, int dk, int dv, cudaStream_t stream) {
+  constexpr int DP = R * kLanes, COLS = kCols * C;
+  const int tch = DP <= 128 ? 16 : 8;
+  const size_t smem = (size_t)2 * (tch * (3 * DP + COLS) + ((tch + 3) & ~3)) * sizeof(float);
+  cudaFuncSetAttribute(delta_recurrence_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid((dv + COLS - 1) / COLS, H, n_entries);
+  ccb_launch(delta_recurrence_kernel<R, C>, grid, dim3(kRecThreads), smem, stream, qn, kn, vv, gg, bb, state, out,
+             cu_q, state_slot, G, H, dk, dv, tch);
+}
+
 CCB_API int ccb_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* gg,
                                  const float* bb, float* state, float* out, const int* cu_q, const int* state_slot,
                                  int n_entries, int G, int H, int dk, int dv, cudaStream_t stream) {
@@ -351,21 +389,18 @@ CCB_API int ccb_delta_recurrence(const float* qn, const float* kn, const float* 
   if (G <= 0 || H <= 0 || H % G || dk <= 0 || dk > 256 || dv <= 0) return CCB_REFUSE_SIZE;
   int R = 1;
   while (R * kLanes < dk) R *= 2;
-  const int DP = R * kLanes;
-  const int tch = DP <= 128 ? 16 : 8;
-  const size_t smem = (size_t)2 * (tch * (3 * DP + kCols) + ((tch + 3) & ~3)) * sizeof(float);
-  dim3 grid((dv + kCols - 1) / kCols, H, n_entries);
-#define CCB_REC(RR)                                                                                              \
-  cudaFuncSetAttribute(delta_recurrence_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-  ccb_launch(delta_recurrence_kernel<RR>, grid, dim3(kRecThreads), smem, stream, qn, kn, vv, gg, bb, state, out, \
-             cu_q, state_slot, G, H, dk, dv, tch)
+  // One column per thread.  Two (the rows of q, k, g read once for both) were slower: 1.11 against 0.99 ms
+  // for 2,048 tokens of 32 heads of 128 x 128, since the kernel is bound by what one warp issues per token
+  // and the larger blocks leave fewer warps per SM.
+#define CCB_REC(RR) \
+  launch_recurrence<RR, 1>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream)
   switch (R) {
     case 1: CCB_REC(1); break;
     case 2: CCB_REC(2); break;
     case 4: CCB_REC(4); break;
     case 8: CCB_REC(8); break;
     case 16: CCB_REC(16); break;
-    default: CCB_REC(32); break;
+    default: launch_recurrence<32, 1>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream); break;
   }
 #undef CCB_REC
   return ccb_launch_status();
