@@ -30,7 +30,8 @@ __device__ __forceinline__ float softplus_f(float x) { return x > 20.f ? x : log
 
 // ---------------------------------------------------------------------------------------------
 // proj [T, ld]: columns q (at oq, G*dk), k (at ok, G*dk), v (at ov, H*dv), b (at ob, H); a [T, lda]: H*dk
-// decay pre-activations.  conv_w float [C, taps] for the channels q|k|v in this order (C = 2 G dk + H dv);
+// decay pre-activations.  conv_w float [taps, C] (tap-major: the channels of a tap side by side) for the
+// channels q|k|v in this order (C = 2 G dk + H dv);
 // conv_state [slots, taps-1, C].
 constexpr int kPrepWarps = 4;
 
@@ -56,7 +57,6 @@ delta_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov,
 
   // convolution + silu of channel c (in the order q | k | v), input column `col` of proj
   auto conv = [&](int c, int col) -> float {
-    const float* w = conv_w + (size_t)c * taps;
     float acc = 0.f;
     for (int j = 0; j < taps; ++j) {  // tap j multiplies the input (taps - 1 - j) tokens back
       const int back = taps - 1 - j;
@@ -64,7 +64,7 @@ delta_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov,
       float x;
       if (li >= 0) x = to_f32(proj[(size_t)(t - back) * ld + col]);
       else x = to_f32(st[(size_t)(taps - 1 + li) * C + c]);
-      acc += w[j] * x;
+      acc += conv_w[(size_t)j * C + c] * x;
     }
     return acc * sigmoid_f(acc);
   };
@@ -102,6 +102,100 @@ delta_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov,
         const float x = to_f32(a[(size_t)t * lda + head * dk + i]) + dt_bias[head * dk + i];
         dst[i] = expf(-rate * softplus_f(x));
       }
+    }
+  }
+}
+
+// The same with four neighbouring channels per lane (16-byte stores, 8- or 16-byte loads): head sizes, column
+// offsets, row strides and the channel count are multiples of 4.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 r = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kPrepWarps * 32)
+delta_prepare_vec_kernel(const T* __restrict__ proj, int ld, int oq, int ok, int ov, int ob, const T* __restrict__ a,
+                         int lda, const float* __restrict__ conv_w, int taps, const T* __restrict__ conv_state,
+                         const float* __restrict__ A_log, const float* __restrict__ dt_bias,
+                         const int* __restrict__ entry_of_token, const int* __restrict__ cu_q,
+                         const int* __restrict__ state_slot, float* __restrict__ qn, float* __restrict__ kn,
+                         float* __restrict__ vv, float* __restrict__ gg, float* __restrict__ bb, int G, int H, int dk,
+                         int dv, float q_mult, float unit_eps) {
+  ccb::pdl_begin();
+  const int t = blockIdx.x;
+  const int e = entry_of_token[t];
+  if (e < 0) return;
+  const int slot = state_slot[e];
+  if (slot < 0) return;
+  const int lt = t - cu_q[e];
+  const int C = 2 * G * dk + H * dv;
+  const T* st = conv_state + (size_t)slot * (taps - 1) * C;
+  const int lane = threadIdx.x & 31;
+
+  // convolution + silu of channels c .. c + 3, input columns col .. col + 3 of proj
+  auto conv4 = [&](int c, int col) -> float4 {
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;
+      const int li = lt - back;
+      const float4 x = li >= 0 ? load4(proj + (size_t)(t - back) * ld + col) : load4(st + (size_t)(taps - 1 + li) * C + c);
+      const float4 w = load4(conv_w + (size_t)j * C + c);
+      acc[0] += w.x * x.x;
+      acc[1] += w.y * x.y;
+      acc[2] += w.z * x.z;
+      acc[3] += w.w * x.w;
+    }
+    return make_float4(acc[0] * sigmoid_f(acc[0]), acc[1] * sigmoid_f(acc[1]), acc[2] * sigmoid_f(acc[2]),
+                       acc[3] * sigmoid_f(acc[3]));
+  };
+
+  const int units = 2 * G + 2 * H;
+  const int u = blockIdx.y * kPrepWarps + (threadIdx.x >> 5);
+  if (u >= units) return;
+  if (u < 2 * G) {
+    const bool is_q = u < G;
+    const int head = is_q ? u : u - G;
+    const int c0 = (is_q ? 0 : G * dk) + head * dk;
+    const int col0 = (is_q ? oq : ok) + head * dk;
+    float* dst = (is_q ? qn : kn) + ((size_t)t * G + head) * dk;
+    float4 y[2];   // key sizes up to 256
+    float ss = 0.f;
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      const int i = 4 * lane + 128 * m;
+      if (i < dk) {
+        y[m] = conv4(c0 + i, col0 + i);
+        ss += y[m].x * y[m].x + y[m].y * y[m].y + y[m].z * y[m].z + y[m].w * y[m].w;
+      }
+    }
+    ss = warp_sum(ss);
+    const float inv = (is_q ? q_mult : 1.0f) / sqrtf(ss + unit_eps);
+#pragma unroll
+    for (int m = 0; m < 2; ++m) {
+      const int i = 4 * lane + 128 * m;
+      if (i < dk)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(y[m].x * inv, y[m].y * inv, y[m].z * inv, y[m].w * inv);
+    }
+  } else if (u < 2 * G + H) {
+    const int head = u - 2 * G;
+    const int c0 = 2 * G * dk + head * dv;
+    float* dst = vv + ((size_t)t * H + head) * dv;
+    for (int i = 4 * lane; i < dv; i += 128) *reinterpret_cast<float4*>(dst + i) = conv4(c0 + i, ov + head * dv + i);
+    if (lane == 0) bb[(size_t)t * H + head] = sigmoid_f(to_f32(proj[(size_t)t * ld + ob + head]));
+  } else {
+    const int head = u - 2 * G - H;
+    const float rate = expf(A_log[head]);
+    float* dst = gg + ((size_t)t * H + head) * dk;
+    for (int i = 4 * lane; i < dk; i += 128) {
+      const float4 x = load4(a + (size_t)t * lda + head * dk + i);
+      const float4 b = load4(dt_bias + head * dk + i);
+      *reinterpret_cast<float4*>(dst + i) =
+          make_float4(expf(-rate * softplus_f(x.x + b.x)), expf(-rate * softplus_f(x.y + b.y)),
+                      expf(-rate * softplus_f(x.z + b.z)), expf(-rate * softplus_f(x.w + b.w)));
     }
   }
 }
@@ -339,6 +433,27 @@ CCB_API int ccb_delta_prepare(const void* proj, int ld, int oq, int ok, int ov, 
   if (T_ <= 0) return 0;
   if (G <= 0 || H <= 0 || H % G || dk <= 0 || dv <= 0 || taps < 1) return CCB_REFUSE_SIZE;
   const dim3 grid(T_, (2 * G + 2 * H + kPrepWarps - 1) / kPrepWarps);
+  const int esz = dtype == CCB_F32 ? 4 : 2;
+  const bool vec = (dk % 4 == 0) && (dv % 4 == 0) && dk <= 256 && (ld % 4 == 0) && (lda % 4 == 0) && (oq % 4 == 0) &&
+                   (ok % 4 == 0) && (ov % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(a) |
+                     reinterpret_cast<uintptr_t>(conv_state)) % (4 * esz) == 0) &&
+                   ((reinterpret_cast<uintptr_t>(qn) | reinterpret_cast<uintptr_t>(kn) | reinterpret_cast<uintptr_t>(vv) |
+                     reinterpret_cast<uintptr_t>(gg) | reinterpret_cast<uintptr_t>(dt_bias) |
+                     reinterpret_cast<uintptr_t>(conv_w)) & 15) == 0;
+  if (vec && dtype == CCB_F32) {
+    ccb_launch(delta_prepare_vec_kernel<float>, grid, dim3(kPrepWarps * 32), 0, stream, (const float*)proj, ld, oq, ok,
+               ov, ob, (const float*)a, lda, conv_w, taps, (const float*)conv_state, A_log, dt_bias, entry_of_token,
+               cu_q, state_slot, qn, kn, vv, gg, bb, G, H, dk, dv, q_mult, unit_eps);
+    return ccb_launch_status();
+  }
+  if (vec && dtype == CCB_BF16) {
+    ccb_launch(delta_prepare_vec_kernel<__nv_bfloat16>, grid, dim3(kPrepWarps * 32), 0, stream,
+               (const __nv_bfloat16*)proj, ld, oq, ok, ov, ob, (const __nv_bfloat16*)a, lda, conv_w, taps,
+               (const __nv_bfloat16*)conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, qn, kn, vv, gg, bb,
+               G, H, dk, dv, q_mult, unit_eps);
+    return ccb_launch_status();
+  }
   if (dtype == CCB_F32)
     ccb_launch(delta_prepare_kernel<float>, grid, dim3(kPrepWarps * 32), 0, stream, (const float*)proj, ld, oq, ok, ov, ob,
                (const float*)a, lda, conv_w, taps, (const float*)conv_state, A_log, dt_bias, entry_of_token, cu_q,

@@ -394,11 +394,11 @@ def delta_prepare(proj, offsets, a, conv_w, taps: int, conv_state, A_log, dt_bia
     """The inputs of the gated delta rule from the projections' rows: convolution + silu of q, k, v (with the
     request's convolution state before the portion), unit q and k per head (q times ``q_mult``),
     beta = sigmoid(b), decay = exp(-exp(A_log) softplus(a + dt_bias)); outputs float.  ``offsets`` = the first
-    columns of q, k, v, b in ``proj``."""
+    columns of q, k, v, b in ``proj``; ``conv_w`` [taps, channels of q|k|v]."""
     _cuda(conv_w, conv_state, A_log, dt_bias, entry_of_token, cu_q, state_slot, qn, kn, vv, gg, bb)
     T = qn.shape[0]
     assert proj.stride(1) == 1 and a.stride(1) == 1 and proj.dtype == a.dtype == conv_state.dtype
-    assert conv_w.dtype == torch.float32 and conv_w.shape == (2 * G * dk + H * dv, taps)
+    assert conv_w.dtype == torch.float32 and conv_w.shape == (taps, 2 * G * dk + H * dv)   # tap-major
     oq, ok, ov, ob = offsets
     _check(lib().ccb_delta_prepare(_p(proj), proj.stride(0), oq, ok, ov, ob, _p(a), a.stride(0), _p(conv_w), taps,
                                    _p(conv_state), _p(A_log), _p(dt_bias), _p(entry_of_token), _p(cu_q),

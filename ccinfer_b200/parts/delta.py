@@ -104,7 +104,8 @@ class ChannelGatedDelta(Mixer):
         self.w_a2[:, :self.a_rank] = a2
         self.w_g2 = torch.zeros((self.v_width, _pad8(self.g_rank)), dtype=rt.dtype, device=rt.device)
         self.w_g2[:, :self.g_rank] = g2
-        self.conv_w = torch.cat([fetch(n["q_conv"]), fetch(n["k_conv"]), fetch(n["v_conv"])], dim=0).float().contiguous()
+        # tap-major: the kernel reads the weights of neighbouring channels of one tap together
+        self.conv_w = torch.cat([fetch(n["q_conv"]), fetch(n["k_conv"]), fetch(n["v_conv"])], dim=0).float().t().contiguous()
         self.A_log = fetch(n["A_log"]).float().contiguous()
         self.dt_bias = fetch(n["dt_bias"]).float().contiguous()
         self.norm_w = fetch(n["norm"]).float().contiguous()

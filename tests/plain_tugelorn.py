@@ -283,6 +283,13 @@ CONFIGS = {
         (_delta(1, 1, 8, 8, 1), _mlp(40, 2.0)),
         (_attn(1, 1, 16, 16, 0.25, q_temp=(1.0, 1), kind="attention_2"), None),
     ]), {1: (4, 4)}, 16),
+    # sizes that are multiples of nothing: width 100, head sizes 20 / 12 and 10 / 6, three heads on one, five
+    # taps, ranks 3 and 7, a window of 5, six rotated coordinates, the whole model looped twice
+    "S": (_model(100, 257, 1e-5, 0.3, [
+        (_attn(3, 1, 20, 12, 0.22, window=5, rot=(6, 3000.0, 1.5)), _mlp(150, 2.0)),
+        (_delta(3, 1, 10, 6, 5), _mlp(90, 4.0)),
+        (_attn(3, 3, 12, 20, 0.3, q_temp=(0.3, 3), kind="attention_2"), None),
+    ], loop=(0, 3, 2)), {1: (3, 7)}, 4),
 }
 
 

@@ -235,7 +235,8 @@ def test_one_layer_of_each_kind(tmp_path, kind, dtype):
 # ---------------------------------------------------------------------------------------------
 # GPU: whole models under every cutting
 # ---------------------------------------------------------------------------------------------
-LENGTHS = {"P": [1, 2, 23, 24, 25, 26, 60, 97], "Q": [3, 69, 70, 71, 72, 140, 200], "R": [1, 15, 16, 17, 18, 33, 64]}
+LENGTHS = {"P": [1, 2, 23, 24, 25, 26, 60, 97], "Q": [3, 69, 70, 71, 72, 140, 200], "R": [1, 15, 16, 17, 18, 33, 64],
+           "S": [1, 4, 5, 6, 7, 21, 50]}
 
 
 @pytest.fixture(scope="module")
