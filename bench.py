@@ -41,7 +41,7 @@ measures another design of the package beside Qwen3 at equal layer sizes (same w
 intermediate size, vocabulary and number of layers; random weights): one prompt of 2,048 and of 8,192 tokens
 in steps of 2,048 (tokens a second) and decode steps of 1 and 8 requests after 2,048-token prompts, replayed
 from CUDA graphs (tokens a second), one JSON line per size.  With --design-profile it only runs a prompt and a
-few eager decode steps of the design, for profilers.  The default line and its contract are untouched.
+few eager decode steps of the design, for profilers.  The default line and what it promises are untouched.
 """
 import argparse
 import json
@@ -281,7 +281,7 @@ def tugelorn_config(size: str, layers: int):
     kinds = [
         {"type": "attention", "mixer": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5,
                                         "mask": {"size": 1024},
-                                        "rot": {"dims": hd, "base": 500000.0, "scaling": {"factor": 8.0}}}},
+                                        "rot": {"dims": hd, "base": 1000000.0, "scaling": {"factor": 4.0}}}},
         {"type": "channel_delta", "mixer": {"heads": H, "kv_heads": H, "dim": hd, "vdim": hd, "conv": 4,
                                             "a_rank": hd, "g_rank": hd}},
         {"type": "attention_2", "mixer": {"heads": H, "kv_heads": G, "dim": hd, "vdim": hd, "scale": hd ** -0.5,

@@ -422,6 +422,53 @@ __global__ void gated_head_rmsnorm_kernel(T* __restrict__ y, const float* __rest
   for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(src[i] * inv * w[i] * sigmoid_f(to_f32(gr[i])));
 }
 
+// The same with four neighbouring channels per lane (dv, the gate's row stride and offset multiples of 4).
+template <typename T> __device__ __forceinline__ void store4(T* p, float4 v);
+template <> __device__ __forceinline__ void store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 r;
+  r.x = *reinterpret_cast<const uint32_t*>(&a);
+  r.y = *reinterpret_cast<const uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = r;
+}
+
+template <typename T>
+__global__ void gated_head_rmsnorm_vec_kernel(T* __restrict__ y, const float* __restrict__ o,
+                                              const T* __restrict__ gate, int ldg, const float* __restrict__ w,
+                                              int rows, int H, int dv, float eps) {
+  ccb::pdl_begin();
+  const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (unit >= rows * H) return;
+  const int lane = threadIdx.x & 31;
+  const int t = unit / H, h = unit - t * H;
+  const float* src = o + (size_t)unit * dv;
+  const T* gr = gate + (size_t)t * ldg + (size_t)h * dv;
+  constexpr int kMax = 4;   // value sizes up to 512
+  float4 x[kMax], g[kMax], ww[kMax];
+  float ss = 0.f;
+#pragma unroll
+  for (int m = 0; m < kMax; ++m) {
+    const int i = 4 * lane + 128 * m;
+    if (i < dv) {
+      x[m] = load4(src + i);
+      g[m] = load4(gr + i);
+      ww[m] = load4(w + i);
+      ss += x[m].x * x[m].x + x[m].y * x[m].y + x[m].z * x[m].z + x[m].w * x[m].w;
+    }
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  T* dst = y + (size_t)unit * dv;
+#pragma unroll
+  for (int m = 0; m < kMax; ++m) {
+    const int i = 4 * lane + 128 * m;
+    if (i < dv)
+      store4<T>(dst + i, make_float4(x[m].x * inv * ww[m].x * sigmoid_f(g[m].x), x[m].y * inv * ww[m].y * sigmoid_f(g[m].y),
+                                     x[m].z * inv * ww[m].z * sigmoid_f(g[m].z), x[m].w * inv * ww[m].w * sigmoid_f(g[m].w)));
+  }
+}
+
 }  // namespace
 
 CCB_API int ccb_delta_prepare(const void* proj, int ld, int oq, int ok, int ov, int ob, const void* a, int lda,
@@ -527,6 +574,20 @@ CCB_API int ccb_gated_head_rmsnorm(void* y, const float* o, const void* gate, in
   if (H <= 0 || dv <= 0) return CCB_REFUSE_SIZE;
   const int units = rows * H;
   dim3 grid((units + 7) / 8);
+  const int esz = dtype == CCB_F32 ? 4 : 2;
+  const bool vec = (dv % 4 == 0) && dv <= 512 && (ldg % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(w)) & 15) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gate)) % (4 * esz)) == 0;
+  if (vec && dtype == CCB_F32) {
+    ccb_launch(gated_head_rmsnorm_vec_kernel<float>, grid, dim3(256), 0, stream, (float*)y, o, (const float*)gate, ldg,
+               w, rows, H, dv, eps);
+    return ccb_launch_status();
+  }
+  if (vec && dtype == CCB_BF16) {
+    ccb_launch(gated_head_rmsnorm_vec_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)y, o,
+               (const __nv_bfloat16*)gate, ldg, w, rows, H, dv, eps);
+    return ccb_launch_status();
+  }
   if (dtype == CCB_F32)
     ccb_launch(gated_head_rmsnorm_kernel<float>, grid, dim3(256), 0, stream, (float*)y, o, (const float*)gate, ldg, w,
                rows, H, dv, eps);

@@ -273,8 +273,8 @@ CONFIGS = {
     # bfloat16) and a value size of 128 beside a key size of 64, rotation without scaling, a window of 70
     "Q": (_model(96, 300, 1e-6, 1.0, [
         (_delta(3, 3, 24, 40, 4), None),
-        (_attn(4, 4, 64, 64, 0.125, q_temp=(0.25, 50), kind="attention_2"), _mlp(160, 2.5)),
-        (_attn(4, 2, 64, 128, 0.11, window=70, rot=(64, 500000.0, None)), None),
+        (_attn(4, 4, 64, 64, 0.13, q_temp=(0.25, 50), kind="attention_2"), _mlp(160, 2.5)),
+        (_attn(4, 2, 64, 128, 0.11, window=70, rot=(64, 250000.0, None)), None),
         (_delta(4, 1, 32, 16, 2), _mlp(64, 1.0)),
     ], loop=(1, 3, 3)), {0: (6, 10), 3: (16, 4)}, 16),
     # no loop at all, a single head everywhere, a window of one page, a convolution of one tap
@@ -285,10 +285,10 @@ CONFIGS = {
     ]), {1: (4, 4)}, 16),
     # sizes that are multiples of nothing: width 100, head sizes 20 / 12 and 10 / 6, three heads on one, five
     # taps, ranks 3 and 7, a window of 5, six rotated coordinates, the whole model looped twice
-    "S": (_model(100, 257, 1e-5, 0.3, [
+    "S": (_model(100, 257, 2e-5, 0.35, [
         (_attn(3, 1, 20, 12, 0.22, window=5, rot=(6, 3000.0, 1.5)), _mlp(150, 2.0)),
         (_delta(3, 1, 10, 6, 5), _mlp(90, 4.0)),
-        (_attn(3, 3, 12, 20, 0.3, q_temp=(0.3, 3), kind="attention_2"), None),
+        (_attn(3, 3, 12, 20, 0.3, q_temp=(0.35, 3), kind="attention_2"), None),
     ], loop=(0, 3, 2)), {1: (3, 7)}, 4),
 }
 

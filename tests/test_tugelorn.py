@@ -107,7 +107,7 @@ def test_heads_are_laid_out_in_a_size_the_kernels_take():
 # ---------------------------------------------------------------------------------------------
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("D", [48, 320, 1000])
+@pytest.mark.parametrize("D", [48, 328, 1000])
 def test_postnorm_residual_kernel(dtype, D):
     from ccinfer_b200 import kernels
     g = torch.Generator().manual_seed(D)
@@ -115,10 +115,10 @@ def test_postnorm_residual_kernel(dtype, D):
     h, add = torch.randn(T, D, generator=g), torch.randn(T, D, generator=g)
     delta = (3 * torch.randn(T, D, generator=g)).to(dtype)
     w1, w2 = 1 + 0.3 * torch.randn(D, generator=g), 1 + 0.3 * torch.randn(D, generator=g)
-    want_h = h.double() + 0.3 * plain.rms_norm(delta.double(), w1.double(), 1e-5) + add.double()
+    want_h = h.double() + 0.4 * plain.rms_norm(delta.double(), w1.double(), 1e-5) + add.double()
     want_y = plain.rms_norm(want_h, w2.double(), 1e-5)
     hd, y = h.cuda(), torch.empty(T, D, dtype=dtype, device="cuda")
-    kernels.postnorm_residual(hd, delta.cuda(), w1.cuda(), 0.3, 1e-5, add=add.cuda(), y=y, w_next=w2.cuda(), eps_next=1e-5)
+    kernels.postnorm_residual(hd, delta.cuda(), w1.cuda(), 0.4, 1e-5, add=add.cuda(), y=y, w_next=w2.cuda(), eps_next=1e-5)
     assert (hd.cpu().double() - want_h).abs().max() < 2e-6 * want_h.abs().max()
     tol = 1e-6 if dtype == torch.float32 else 8e-3
     assert (y.cpu().double() - want_y).abs().max() < tol * want_y.abs().max()
@@ -143,9 +143,9 @@ def test_clamped_glu_kernel(dtype, F, block):
     else:
         gu = torch.cat([gate, up], dim=1)
     act = torch.empty(5, F, dtype=dtype, device="cuda")
-    kernels.clamped_glu(act, gu.contiguous().cuda(), block, 2.0, 1.702, 1.0)
-    want = plain.clamped_glu(gate.double(), up.double(), 2.0)
-    assert (act.cpu().double() - want).abs().max() < (1e-6 if dtype == torch.float32 else 2e-2)
+    kernels.clamped_glu(act, gu.contiguous().cuda(), block, 2.5, 1.702, 1.0)
+    want = plain.clamped_glu(gate.double(), up.double(), 2.5)
+    assert (act.cpu().double() - want).abs().max() < (1e-6 if dtype == torch.float32 else 1e-2) * want.abs().max()
 
 
 @gpu
@@ -317,7 +317,7 @@ def test_a_far_key_decides(tmp_path):
     far place among 300 and token 1 at the end: the last position's logits follow the far token's value, and
     dropping or misplacing its key would change them by their own size.  The far place is the first token, the
     last of a page, the first of the next, and the middle."""
-    cfg = plain._model(32, 64, 1e-5, 1.0, [(plain._attn(2, 1, 16, 16, 1.0, q_temp=(0.2, 64), kind="attention_2"), None)])
+    cfg = plain._model(32, 64, 1e-5, 1.0, [(plain._attn(2, 1, 16, 16, 1.0, q_temp=(0.2, 48), kind="attention_2"), None)])
     d = str(tmp_path / "far")
 
     def edit(w):
