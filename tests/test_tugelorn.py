@@ -381,3 +381,64 @@ def test_greedy_generation_through_the_entry_point(models, dtype):
                 assert row[t] >= row.max() - 0.05 * row.abs().max()
                 toks.append(t)
     assert all(pool.used_pages == 0 for pool in llm.engine.cache.pools)
+
+
+@gpu
+def test_the_programs_as_a_user_calls_them(models, tmp_path):
+    """bin/ccinfer: greedy tokens of a model folder, and a random model written from a configuration (which
+    must carry the delta rule's ranks) that generates the same tokens as the same configuration drawn on the
+    device; bin/trace_run: a mixed trace over four request slots, its files against the plain logits."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    d, cfg, w, reqs, ref, page = models["R", "float32"]
+    exe = [sys.executable, os.path.join(root, "bin", "ccinfer")]
+    prompt = list(reqs.values())[2]
+    r = subprocess.run(exe + ["--model-path", d, "--dtype", "float32", "--page-size", str(page), "--kv-tokens", "256",
+                              "--max-tokens", "6", "--prompt-ids", ",".join(map(str, prompt))],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[0])["token_ids"] == plain.greedy(cfg, w, prompt, 6)
+
+    from ccinfer_b200.config.tugelorn import TugelornConfig
+    full = TugelornConfig.from_json(cfg).with_shapes(plain.tensor_shapes(cfg, plain.CONFIGS["R"][1])).to_json()
+    cj = str(tmp_path / "config.json")
+    with open(cj, "w") as f:
+        json.dump(full, f)
+    common = ["--dtype", "float32", "--kv-tokens", "256", "--max-tokens", "5", "--random-prompts", "9,4",
+              "--weights-seed", "5", "--weights-std", "0.3"]
+    a = subprocess.run(exe + ["--random-config", cj] + common, capture_output=True, text=True, timeout=600)
+    assert a.returncode == 0, a.stderr[-2000:]
+    made = str(tmp_path / "made")
+    wr = subprocess.run(exe + ["--model-path", made, "--write-random-model", cj, "--weights-seed", "5",
+                               "--weights-std", "0.3"], capture_output=True, text=True, timeout=600)
+    assert wr.returncode == 0, wr.stderr[-2000:]
+    b = subprocess.run(exe + ["--model-path", made] + common, capture_output=True, text=True, timeout=600)
+    assert b.returncode == 0, b.stderr[-2000:]
+    assert a.stdout == b.stdout and len(a.stdout.strip().splitlines()) == 2
+    with open(cj, "w") as f:
+        json.dump(cfg, f)   # without the ranks no random model can be drawn: the error says so
+    bad = subprocess.run(exe + ["--random-config", cj] + common, capture_output=True, text=True, timeout=600)
+    assert bad.returncode == 2 and "ranks" in bad.stderr
+
+    steps = helpers.trace_mixed(reqs, max_live=4, seed=3)
+    pool = helpers.max_live_tokens(steps)
+    out_dir = tmp_path / "out"
+    lines = "".join(json.dumps({"step": i, **st}) + "\n" for i, st in enumerate(steps))
+    t = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", "float32", "--out",
+                        str(out_dir), "--max-tokens", str(pool)], input=lines, capture_output=True, text=True,
+                       timeout=600)
+    assert t.returncode == 0, t.stderr[-2000:]
+    assert t.stdout.split() == [x for i in range(len(steps)) for x in ("done", str(i))]
+    rows, seen = {}, {rid: 0 for rid in reqs}
+    for i, st in enumerate(steps):
+        n_want = sum(len(e["want"]) for e in st["entries"])
+        arr = np.fromfile(out_dir / f"{i}.f32", dtype="<f4").reshape(n_want, cfg["vocab"])
+        at = 0
+        for e in st["entries"]:
+            for wnt in e["want"]:
+                rows[(e["id"], seen[e["id"]] + wnt)] = arr[at]
+                at += 1
+            seen[e["id"]] += len(e["tokens"])
+    assert len(rows) == sum(len(x) for x in reqs.values())
+    helpers.compare(rows, ref, TOL32, "trace_run")
