@@ -47,6 +47,9 @@ struct FusedQkv {
   const float* inv_freq;      // [HD / 2] rotation frequencies, or null
   __nv_bfloat16* k_cache;     // where the new key and value go; null when the cache belongs to another layer
   __nv_bfloat16* v_cache;     // (that layer has written this position already)
+  const float* bias;          // [(nq + 2 nkv) * HD] added to the product's rows before anything else, or null
+  float qt_coef;              // queries times 1 + qt_coef * ln(floor((p + 1) / qt_every) + 1) after the rotation
+  int qt_every;               // 0: no such factor
 };
 
 // (cos, sin) of position * inv_freq[i], or (1, 0) without rotation
@@ -165,7 +168,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
           const float2 hi = valid ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + c + 8))
                                   : make_float2(0.f, 0.f);
           x[ks][0] = lo.x; x[ks][1] = lo.y; x[ks][2] = hi.x; x[ks][3] = hi.y;
-          ss += lo.x * lo.x + lo.y * lo.y + hi.x * hi.x + hi.y * hi.y;
+          if (fq.bias != nullptr && valid) {
+            const float* bh = fq.bias + (size_t)(h0 + gid + 8 * rh) * HD + c;
+            x[ks][0] += bh[0]; x[ks][1] += bh[1]; x[ks][2] += bh[8]; x[ks][3] += bh[9];
+          }
+          ss += x[ks][0] * x[ks][0] + x[ks][1] * x[ks][1] + x[ks][2] * x[ks][2] + x[ks][3] * x[ks][3];
         }
         if (fq.q_w != nullptr) {
           ss += __shfl_xor_sync(0xffffffffu, ss, 1);
@@ -193,10 +200,11 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
             }
           }
         }
+        const float qs = fq.qt_every > 0 ? 1.0f + fq.qt_coef * logf((float)((p + 1) / fq.qt_every) + 1.0f) : 1.0f;
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
-          qa[ks][rh] = pack_bf16(x[ks][0], x[ks][1]);
-          qa[ks][2 + rh] = pack_bf16(x[ks][2], x[ks][3]);
+          qa[ks][rh] = pack_bf16(x[ks][0] * qs, x[ks][1] * qs);
+          qa[ks][2 + rh] = pack_bf16(x[ks][2] * qs, x[ks][3] * qs);
         }
       }
       if (warp == 0) {   // the same queries for the warp that adds the new key at the end
@@ -379,6 +387,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap tmK, const __gri
     for (int c = 0; c < CPL; ++c) {
       kx[c] = __bfloat162float(krow[col0 + c]);
       vb[c] = vrow[col0 + c];
+      if (fq.bias != nullptr) {
+        kx[c] += fq.bias[(size_t)(nq + kvh) * HD + col0 + c];
+        vb[c] = __float2bfloat16_rn(__bfloat162float(vb[c]) + fq.bias[(size_t)(nq + nkv + kvh) * HD + col0 + c]);
+      }
       ss += kx[c] * kx[c];
     }
     if (fq.k_w != nullptr) {
@@ -624,6 +636,8 @@ CCB_API int ccb_attention_decode_tma(const void* q, const void* k_cache, const v
 // per-head norms (q_w, k_w: [hd] floats or null) and the rotate-half rotation (inv_freq: [hd / 2] or null)
 // at positions[t], writes the row's key and value to their page (write_kv != 0; with 0 the cache belongs to
 // another layer that has written the position already) and attends over positions <= positions[t].
+// bias ([(nq + 2 nkv) hd] floats or null) is added to the rows first; qt_every > 0 scales the queries by
+// 1 + qt_coef ln(floor((p + 1) / qt_every) + 1) after the rotation.
 // qk_norm_rope_kv_write is not needed for such rows.
 CCB_API int ccb_attention_decode_tma_fused(const void* qkv, int qkv_stride, void* k_cache, void* v_cache, void* out,
                                            float* part_acc, float* part_ml, const int* positions,
@@ -631,8 +645,10 @@ CCB_API int ccb_attention_decode_tma_fused(const void* qkv, int qkv_stride, void
                                            int n_entries, int row0, int n_rows, int nq, int nkv, int hd,
                                            int page_size, int num_pages, int window, float scale, int num_splits,
                                            const float* q_w, const float* k_w, float eps, const float* inv_freq,
-                                           int write_kv, int* counters, int* status, cudaStream_t stream) {
+                                           int write_kv, const float* bias, float qt_coef, int qt_every,
+                                           int* counters, int* status, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  if (qt_every < 0 || (bias != nullptr && !write_kv)) return CCB_REFUSE_ARG;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || bt_stride <= 0 || num_splits <= 0 || num_splits > 64 ||
       page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0 || (qkv_stride & 1) ||
       qkv_stride < (nq + (write_kv ? 2 * nkv : 0)) * hd ||
@@ -649,6 +665,9 @@ CCB_API int ccb_attention_decode_tma_fused(const void* qkv, int qkv_stride, void
   fq.inv_freq = inv_freq;
   fq.k_cache = write_kv ? (__nv_bfloat16*)k_cache : nullptr;
   fq.v_cache = write_kv ? (__nv_bfloat16*)v_cache : nullptr;
+  fq.bias = bias;
+  fq.qt_coef = qt_coef;
+  fq.qt_every = qt_every;
   if (hd == 128)
     return launch<128, true>(nullptr, fq, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
                              block_table, bt_stride, n_entries, row0, n_rows, nq, nkv, page_size, num_pages, window,

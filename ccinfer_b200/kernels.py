@@ -91,7 +91,7 @@ _SIGNATURES = {
     "ccb_attention_decode_tma_fused": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                        c_int, c_int, c_float, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int,
-                                       c_void_p, c_void_p, c_void_p],
+                                       c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p],
     "ccb_attention_prefill_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p,
                                   c_void_p],
@@ -599,13 +599,17 @@ def attention_prefill_mma(q, k_cache, v_cache, out, cu_q, pos0, block_table, ent
 def attention_decode_tma_fused(qkv, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token,
                                block_table, n_entries: int, row0: int, n_rows: int, nq: int, window: int,
                                scale: float, num_splits: int, q_norm_w, k_norm_w, eps: float, inv_freq,
-                               write_kv: bool = True, status=None, merge_counters=None) -> None:
+                               write_kv: bool = True, status=None, merge_counters=None, bias=None,
+                               q_temperature=None) -> None:
     """attention_decode_tma for rows of ONE new token each, straight from the q|k|v product ``qkv``
     [T, (nq + 2 nkv) * hd] (only the nq query heads when ``write_kv`` is false): the kernel norms and rotates
     the queries itself and, with ``write_kv``, also the row's key, which it writes with the value to their
-    page and attends to.  qk_norm_rope_kv_write is not needed for these rows."""
+    page and attends to.  qk_norm_rope_kv_write is not needed for these rows.  ``bias`` and ``q_temperature``
+    as for ``qkv_bias_rope_kv_write``."""
     _cuda(qkv, k_cache, v_cache, out, part_acc, part_ml, positions, entry_of_token, block_table, status,
-          merge_counters, q_norm_w, k_norm_w, inv_freq)
+          merge_counters, q_norm_w, k_norm_w, inv_freq, bias)
+    assert bias is None or (write_kv and bias.dtype == torch.float32
+                            and bias.numel() == (nq + 2 * k_cache.shape[1]) * k_cache.shape[3])
     T = qkv.shape[0]
     num_pages, nkv, page_size, hd = k_cache.shape
     assert out.shape == (T, nq, hd) and qkv.stride(1) == 1
@@ -624,7 +628,9 @@ def attention_decode_tma_fused(qkv, k_cache, v_cache, out, part_acc, part_ml, po
         _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(out), _p(part_acc), _p(part_ml), _p(positions),
         _p(entry_of_token), _p(block_table), block_table.stride(0), n_entries, row0, n_rows, nq, nkv, hd, page_size,
         num_pages, int(window), float(scale), num_splits, _p(q_norm_w), _p(k_norm_w), float(eps), _p(inv_freq),
-        1 if write_kv else 0, _p(merge_counters), _p(status), _stream()), "attention_decode_tma_fused")
+        1 if write_kv else 0, _p(bias), float(q_temperature[0]) if q_temperature else 0.0,
+        int(q_temperature[1]) if q_temperature else 0, _p(merge_counters), _p(status), _stream()),
+        "attention_decode_tma_fused")
     if num_splits > 1 and merge_counters is None:
         counters.own += 1  # the merge kernel
 

@@ -18,7 +18,7 @@ Beyond the reference: biases of the three projections (names q_bias, k_bias,
 v_bias; added by the kernel that rotates q and k and writes the cache), a
 value size that differs from the query/key size (``value_dim``), a score scale
 of the model's choosing, and a query temperature stated by the position
-encoding.  The attention kernels know one head size; with ``value_dim`` given,
+encoding (both also inside the fused decode attention).  The attention kernels know one head size; with ``value_dim`` given,
 the heads of q, k and v are laid out in the smallest size the kernels take that
 holds both (a multiple of 16), the added coordinates being zero rows of the
 projections and zero columns of the output projection: zeros in q and k add
@@ -199,7 +199,7 @@ class GroupedQueryAttention(Mixer):
         """A step of single tokens only, on the path of the TMA decode kernel (bfloat16, head size 64 or 128,
         a page size it takes), with few enough rows that every block redoing the queries' norm and rotation
         costs less than a kernel of its own."""
-        return (self.bias is None and self.position.query_temperature() is None and not self.float_weights
+        return (not self.float_weights and (self.bias is None or self.own_kv)
                 and self.rt.dtype == torch.bfloat16 and self.hd in kernels.DECODE_MMA_HEAD_SIZES
                 and kernels.attention_decode_tma_fits(self.hd, g.page_size)
                 and step.n_single == step.n_entries == step.n_tokens
@@ -226,7 +226,8 @@ class GroupedQueryAttention(Mixer):
                 g.block_table, step.n_entries, 0, T, self.nq, self.window or 0, self.scale, splits,
                 self.q_norm_w, self.k_norm_w, self.qk_norm_eps if self.qk_norm_eps is not None else 1.0,
                 self.position.rotary_table(), write_kv=self.own_kv, status=rt.status,
-                merge_counters=rt.merge_counters if splits >= self.MERGE_IN_KERNEL_MIN_SPLITS else None)
+                merge_counters=rt.merge_counters if splits >= self.MERGE_IN_KERNEL_MIN_SPLITS else None,
+                bias=self.bias, q_temperature=self.position.query_temperature())
         else:
             q = rt.scratch.get("attn_q", (rt.max_tokens, self.nq, self.hd), rt.dtype)[:T]
             args = (qkv, q, cache.k if self.own_kv else None, cache.v if self.own_kv else None, step.positions,
