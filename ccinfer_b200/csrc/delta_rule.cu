@@ -552,8 +552,10 @@ CCB_API int ccb_delta_recurrence(const float* qn, const float* kn, const float* 
   int R = 1;
   while (R * kLanes < dk) R *= 2;
   // One column per thread.  Two (the rows of q, k, g read once for both) were slower: 1.11 against 0.99 ms
-  // for 2,048 tokens of 32 heads of 128 x 128, since the kernel is bound by what one warp issues per token
-  // and the larger blocks leave fewer warps per SM.
+  // for 2,048 tokens of 32 heads of 128 x 128, since the kernel is bound by the latency of what one warp issues
+  // per token (with a warp per scheduler an instruction issues every third cycle) and the larger blocks leave
+  // fewer warps per SM.  Sixteen lanes a column (twice the warps, one shuffle more per sum) were no faster
+  // either (1.03 ms).
 #define CCB_REC(RR) \
   launch_recurrence<RR, 1>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream)
   switch (R) {
