@@ -50,6 +50,13 @@ def _builtin():
                               complete_config=lambda cfg, shapes: cfg.with_shapes(shapes))
 
 
+    if "Dufizen" not in _REGISTRY:
+        from ..architectures import dufizen
+        from .dufizen import DufizenConfig
+        register_architecture("Dufizen", DufizenConfig.from_json, dufizen.build_plan,
+                              complete_config=lambda cfg, shapes: cfg.with_shapes(shapes))
+
+
 def architecture_of(config_json: dict) -> Architecture:
     _builtin()
     archs = config_json.get("architectures")

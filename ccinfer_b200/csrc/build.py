@@ -34,6 +34,9 @@ GROUPS = {
         "norm.cu",
         "rope_kv.cu",
         "delta_rule.cu",
+        "linear_attention.cu",
+        "latent_attention.cu",
+        "moe.cu",
         "attention_generic.cu",
         "attention_split.cu",
         "attention_decode_mma.cu",

@@ -269,7 +269,10 @@ __device__ __forceinline__ float lanes_sum(float v) {
 // state before the write (o = (gS)^T q + u (k . q), which is the read-out after the write), their sums over
 // the lanes run side by side, each sum over a lane's rows is four shorter chains, and the read-out is off the
 // chain altogether.
-template <int R, int C>
+//
+// DELTA false: the plain gated recurrence  S <- diag(g_t) S + k_t v_t^T,  o_t = S^T q_t  (gated linear
+// attention): u = v, so S^T k and beta are not needed and the chain per token is the decay and one update.
+template <int R, int C, bool DELTA>
 __global__ void __launch_bounds__(kRecThreads)
 delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
                         const float* __restrict__ gg, const float* __restrict__ bb, float* __restrict__ state,
@@ -322,7 +325,8 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       if (gc < dv) cp_async4(sv + i, vv + ((size_t)(r0 + t0 + tt) * H + head) * dv + gc);
     }
     float* sb = sv + tch * COLS;
-    for (int i = threadIdx.x; i < cnt; i += kRecThreads) cp_async4(sb + i, bb + (size_t)(r0 + t0 + i) * H + head);
+    if (DELTA)
+      for (int i = threadIdx.x; i < cnt; i += kRecThreads) cp_async4(sb + i, bb + (size_t)(r0 + t0 + i) * H + head);
     cp_async_commit();
   };
 
@@ -352,7 +356,7 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
       Rows<R>::load(base + tt * DP, lane, qr);
       Rows<R>::load(base + tch * DP + tt * DP, lane, kr);
       Rows<R>::load(base + 2 * tch * DP + tt * DP, lane, gr);
-      const float beta = sb[tt];
+      const float beta = DELTA ? sb[tt] : 1.f;
       constexpr int P = R < 4 ? R : 4;   // partial sums per lane
       float kqp[P];
 #pragma unroll
@@ -371,21 +375,23 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
 #pragma unroll
         for (int i = 0; i < R; ++i) {
           S[c][i] *= gr[i];
-          dkp[i % P] = fmaf(S[c][i], kr[i], dkp[i % P]);
+          if (DELTA) dkp[i % P] = fmaf(S[c][i], kr[i], dkp[i % P]);
           dqp[i % P] = fmaf(S[c][i], qr[i], dqp[i % P]);
         }
         dkk[c] = dkp[0], dqq[c] = dqp[0];
 #pragma unroll
         for (int p = 1; p < P; ++p) dkk[c] += dkp[p], dqq[c] += dqp[p];
       }
+      if (DELTA) {
 #pragma unroll
-      for (int c = 0; c < C; ++c) dkk[c] = lanes_sum(dkk[c]);
+        for (int c = 0; c < C; ++c) dkk[c] = lanes_sum(dkk[c]);
+      }
       kq = lanes_sum(kq);
 #pragma unroll
       for (int c = 0; c < C; ++c) dqq[c] = lanes_sum(dqq[c]);
 #pragma unroll
       for (int c = 0; c < C; ++c) {
-        const float u = beta * (sv[tt * COLS + cl * C + c] - dkk[c]);
+        const float u = DELTA ? beta * (sv[tt * COLS + cl * C + c] - dkk[c]) : sv[tt * COLS + cl * C + c];
 #pragma unroll
         for (int i = 0; i < R; ++i) S[c][i] = fmaf(kr[i], u, S[c][i]);
         if (lane == c % kLanes && col0 + c < dv)
@@ -403,8 +409,11 @@ delta_recurrence_kernel(const float* __restrict__ qn, const float* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------------------------
-// y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * sigmoid(gate[t, h, :]); one warp per (t, h)
-template <typename T>
+// y[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w[:] * sigmoid(gate[t, h, :]); one warp per (t, h).
+// SILU: the gate is gate * sigmoid(gate) instead.
+template <bool SILU> __device__ __forceinline__ float gate_f(float x) { return SILU ? x * sigmoid_f(x) : sigmoid_f(x); }
+
+template <typename T, bool SILU>
 __global__ void gated_head_rmsnorm_kernel(T* __restrict__ y, const float* __restrict__ o, const T* __restrict__ gate,
                                           int ldg, const float* __restrict__ w, int rows, int H, int dv, float eps) {
   ccb::pdl_begin();
@@ -419,7 +428,7 @@ __global__ void gated_head_rmsnorm_kernel(T* __restrict__ y, const float* __rest
   const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
   const T* gr = gate + (size_t)t * ldg + (size_t)h * dv;
   T* dst = y + (size_t)unit * dv;
-  for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(src[i] * inv * w[i] * sigmoid_f(to_f32(gr[i])));
+  for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(src[i] * inv * w[i] * gate_f<SILU>(to_f32(gr[i])));
 }
 
 // The same with four neighbouring channels per lane (dv, the gate's row stride and offset multiples of 4).
@@ -433,7 +442,7 @@ template <> __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<uint2*>(p) = r;
 }
 
-template <typename T>
+template <typename T, bool SILU>
 __global__ void gated_head_rmsnorm_vec_kernel(T* __restrict__ y, const float* __restrict__ o,
                                               const T* __restrict__ gate, int ldg, const float* __restrict__ w,
                                               int rows, int H, int dv, float eps) {
@@ -464,8 +473,8 @@ __global__ void gated_head_rmsnorm_vec_kernel(T* __restrict__ y, const float* __
   for (int m = 0; m < kMax; ++m) {
     const int i = 4 * lane + 128 * m;
     if (i < dv)
-      store4<T>(dst + i, make_float4(x[m].x * inv * ww[m].x * sigmoid_f(g[m].x), x[m].y * inv * ww[m].y * sigmoid_f(g[m].y),
-                                     x[m].z * inv * ww[m].z * sigmoid_f(g[m].z), x[m].w * inv * ww[m].w * sigmoid_f(g[m].w)));
+      store4<T>(dst + i, make_float4(x[m].x * inv * ww[m].x * gate_f<SILU>(g[m].x), x[m].y * inv * ww[m].y * gate_f<SILU>(g[m].y),
+                                     x[m].z * inv * ww[m].z * gate_f<SILU>(g[m].z), x[m].w * inv * ww[m].w * gate_f<SILU>(g[m].w)));
   }
 }
 
@@ -531,22 +540,23 @@ CCB_API int ccb_conv_state_update(const void* proj, int ld, int oq, int ok, int 
   return ccb_launch_status();
 }
 
-template <int R, int C>
+template <int R, int C, bool DELTA>
 static void launch_recurrence(const float* qn, const float* kn, const float* vv, const float* gg, const float* bb,
                               float* state, float* out, const int* cu_q, const int* state_slot, int n_entries, int G,
                               int H, int dk, int dv, cudaStream_t stream) {
   constexpr int DP = R * kLanes, COLS = kCols * C;
   const int tch = DP <= 128 ? 16 : 8;
   const size_t smem = (size_t)2 * (tch * (3 * DP + COLS) + ((tch + 3) & ~3)) * sizeof(float);
-  cudaFuncSetAttribute(delta_recurrence_kernel<R, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  cudaFuncSetAttribute(delta_recurrence_kernel<R, C, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   dim3 grid((dv + COLS - 1) / COLS, H, n_entries);
-  ccb_launch(delta_recurrence_kernel<R, C>, grid, dim3(kRecThreads), smem, stream, qn, kn, vv, gg, bb, state, out,
+  ccb_launch(delta_recurrence_kernel<R, C, DELTA>, grid, dim3(kRecThreads), smem, stream, qn, kn, vv, gg, bb, state, out,
              cu_q, state_slot, G, H, dk, dv, tch);
 }
 
-CCB_API int ccb_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* gg,
-                                 const float* bb, float* state, float* out, const int* cu_q, const int* state_slot,
-                                 int n_entries, int G, int H, int dk, int dv, cudaStream_t stream) {
+template <bool DELTA>
+static int pick_recurrence(const float* qn, const float* kn, const float* vv, const float* gg, const float* bb,
+                           float* state, float* out, const int* cu_q, const int* state_slot, int n_entries, int G,
+                           int H, int dk, int dv, cudaStream_t stream) {
   if (n_entries <= 0) return 0;
   if (G <= 0 || H <= 0 || H % G || dk <= 0 || dk > 256 || dv <= 0) return CCB_REFUSE_SIZE;
   int R = 1;
@@ -557,46 +567,63 @@ CCB_API int ccb_delta_recurrence(const float* qn, const float* kn, const float* 
   // fewer warps per SM.  Sixteen lanes a column (twice the warps, one shuffle more per sum) were no faster
   // either (1.03 ms).
 #define CCB_REC(RR) \
-  launch_recurrence<RR, 1>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream)
+  launch_recurrence<RR, 1, DELTA>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream)
   switch (R) {
     case 1: CCB_REC(1); break;
     case 2: CCB_REC(2); break;
     case 4: CCB_REC(4); break;
     case 8: CCB_REC(8); break;
     case 16: CCB_REC(16); break;
-    default: launch_recurrence<32, 1>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream); break;
+    default: CCB_REC(32); break;
   }
 #undef CCB_REC
   return ccb_launch_status();
 }
 
+CCB_API int ccb_delta_recurrence(const float* qn, const float* kn, const float* vv, const float* gg,
+                                 const float* bb, float* state, float* out, const int* cu_q, const int* state_slot,
+                                 int n_entries, int G, int H, int dk, int dv, cudaStream_t stream) {
+  return pick_recurrence<true>(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries, G, H, dk, dv, stream);
+}
+
+// The plain gated recurrence (no correction by what the state already holds): S <- diag(g) S + k v^T, o = S^T q.
+CCB_API int ccb_gated_linear_recurrence(const float* qn, const float* kn, const float* vv, const float* gg,
+                                        float* state, float* out, const int* cu_q, const int* state_slot,
+                                        int n_entries, int G, int H, int dk, int dv, cudaStream_t stream) {
+  return pick_recurrence<false>(qn, kn, vv, gg, nullptr, state, out, cu_q, state_slot, n_entries, G, H, dk, dv,
+                                stream);
+}
+
+template <typename T, bool SILU>
+static void launch_head_norm(bool vec, dim3 grid, void* y, const float* o, const void* gate, int ldg, const float* w,
+                             int rows, int H, int dv, float eps, cudaStream_t stream) {
+  if (vec)
+    ccb_launch(gated_head_rmsnorm_vec_kernel<T, SILU>, grid, dim3(256), 0, stream, (T*)y, o, (const T*)gate, ldg, w,
+               rows, H, dv, eps);
+  else
+    ccb_launch(gated_head_rmsnorm_kernel<T, SILU>, grid, dim3(256), 0, stream, (T*)y, o, (const T*)gate, ldg, w, rows,
+               H, dv, eps);
+}
+
+// gate_act 0: sigmoid(gate); 1: gate * sigmoid(gate)
 CCB_API int ccb_gated_head_rmsnorm(void* y, const float* o, const void* gate, int ldg, const float* w, int rows,
-                                   int H, int dv, float eps, int dtype, cudaStream_t stream) {
+                                   int H, int dv, float eps, int gate_act, int dtype, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (H <= 0 || dv <= 0) return CCB_REFUSE_SIZE;
+  if (H <= 0 || dv <= 0 || gate_act < 0 || gate_act > 1) return CCB_REFUSE_SIZE;
   const int units = rows * H;
   dim3 grid((units + 7) / 8);
   const int esz = dtype == CCB_F32 ? 4 : 2;
   const bool vec = (dv % 4 == 0) && dv <= 512 && (ldg % 4 == 0) &&
                    ((reinterpret_cast<uintptr_t>(o) | reinterpret_cast<uintptr_t>(w)) & 15) == 0 &&
                    ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(gate)) % (4 * esz)) == 0;
-  if (vec && dtype == CCB_F32) {
-    ccb_launch(gated_head_rmsnorm_vec_kernel<float>, grid, dim3(256), 0, stream, (float*)y, o, (const float*)gate, ldg,
-               w, rows, H, dv, eps);
-    return ccb_launch_status();
-  }
-  if (vec && dtype == CCB_BF16) {
-    ccb_launch(gated_head_rmsnorm_vec_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)y, o,
-               (const __nv_bfloat16*)gate, ldg, w, rows, H, dv, eps);
-    return ccb_launch_status();
-  }
-  if (dtype == CCB_F32)
-    ccb_launch(gated_head_rmsnorm_kernel<float>, grid, dim3(256), 0, stream, (float*)y, o, (const float*)gate, ldg, w,
-               rows, H, dv, eps);
-  else if (dtype == CCB_BF16)
-    ccb_launch(gated_head_rmsnorm_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, (__nv_bfloat16*)y, o,
-               (const __nv_bfloat16*)gate, ldg, w, rows, H, dv, eps);
-  else
+  if (dtype == CCB_F32) {
+    if (gate_act) launch_head_norm<float, true>(vec, grid, y, o, gate, ldg, w, rows, H, dv, eps, stream);
+    else launch_head_norm<float, false>(vec, grid, y, o, gate, ldg, w, rows, H, dv, eps, stream);
+  } else if (dtype == CCB_BF16) {
+    if (gate_act) launch_head_norm<__nv_bfloat16, true>(vec, grid, y, o, gate, ldg, w, rows, H, dv, eps, stream);
+    else launch_head_norm<__nv_bfloat16, false>(vec, grid, y, o, gate, ldg, w, rows, H, dv, eps, stream);
+  } else {
     return CCB_REFUSE_DTYPE;
+  }
   return ccb_launch_status();
 }

@@ -219,3 +219,90 @@ CCB_API int ccb_clamped_glu(void* act, const void* gate_up, int T_, int F, int b
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// out[t, :] = [a[t, :] | b[t, :]] in the storage type: two float streams side by side as the rows of a product.
+template <typename T>
+__global__ void concat_cast_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
+                                   int D, size_t total) {
+  ccb::pdl_begin();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / (2 * (size_t)D);
+    const int c = (int)(i - t * 2 * D);
+    out[i] = from_f32<T>(c < D ? a[t * D + c] : b[t * D + c - D]);
+  }
+}
+
+CCB_API int ccb_concat_cast(void* out, const float* a, const float* b, int rows, int D, int dtype,
+                            cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (D <= 0) return CCB_REFUSE_SIZE;
+  const size_t total = (size_t)rows * 2 * D;
+  const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
+  if (dtype == CCB_F32)
+    ccb_launch(concat_cast_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, a, b, D, total);
+  else if (dtype == CCB_BF16)
+    ccb_launch(concat_cast_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, a, b, D, total);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
+
+// h[t, :] += row[:] (float): one vector added to every row of the stream.
+__global__ void add_row_kernel(float* __restrict__ h, const float* __restrict__ row, int D, size_t total) {
+  ccb::pdl_begin();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    h[i] += row[i % D];
+}
+
+CCB_API int ccb_add_row(float* h, const float* row, int rows, int D, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (D <= 0) return CCB_REFUSE_SIZE;
+  const size_t total = (size_t)rows * D;
+  const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
+  ccb_launch(add_row_kernel, dim3(blocks), dim3(256), 0, stream, h, row, D, total);
+  return ccb_launch_status();
+}
+
+// g[t, j] = gelu_tanh(g[t, j]) * table[ids[t], off + j], j < n: a gate times the token's own row of a second
+// embedding table.  gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), in float.
+// Token ids as in embed_gather (-1 - s: the token last sampled for request slot s).
+template <typename T>
+__global__ void gelu_gate_rows_kernel(T* __restrict__ g, int ldg, const T* __restrict__ table, int ldt, int off,
+                                      const int* __restrict__ ids, int n, int V, const int* __restrict__ pending,
+                                      int n_pending, size_t total, int* status) {
+  ccb::pdl_begin();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / n;
+    const int j = (int)(i - t * n);
+    int id = ids[t];
+    if (id < 0 && pending != nullptr && -1 - id < n_pending) id = pending[-1 - id];
+    T* p = g + t * ldg + j;
+    if (id < 0 || id >= V) {
+      set_status(status, CCB_ST_BAD_TOKEN);
+      *p = from_f32<T>(0.f);
+      continue;
+    }
+    const float z = to_f32(*p);
+    const float u = 0.7978845608028654f * (z + 0.044715f * z * z * z);
+    *p = from_f32<T>(0.5f * z * (1.f + tanhf(u)) * to_f32(table[(size_t)id * ldt + off + j]));
+  }
+}
+
+CCB_API int ccb_gelu_gate_rows(void* g, int ldg, const void* table, int ldt, int off, const int* ids, int rows, int n,
+                               int V, const int* pending, int n_pending, int dtype, int* status,
+                               cudaStream_t stream) {
+  if (rows <= 0 || n <= 0) return 0;
+  if (V <= 0 || off < 0 || off + n > ldt || ldg < n) return CCB_REFUSE_SIZE;
+  const size_t total = (size_t)rows * n;
+  const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
+  if (dtype == CCB_F32)
+    ccb_launch(gelu_gate_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)g, ldg, (const float*)table,
+               ldt, off, ids, n, V, pending, n_pending, total, status);
+  else if (dtype == CCB_BF16)
+    ccb_launch(gelu_gate_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)g, ldg,
+               (const __nv_bfloat16*)table, ldt, off, ids, n, V, pending, n_pending, total, status);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}

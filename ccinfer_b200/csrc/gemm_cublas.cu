@@ -42,3 +42,21 @@ CCB_API int ccb_gemm_bf16(void* handle, void* C, const void* A, const void* W, i
                     CUBLAS_GEMM_DEFAULT);
   return st == CUBLAS_STATUS_SUCCESS ? 0 : 1000 + (int)st;
 }
+
+// The same product for a batch of equal shapes whose operands lie at fixed strides (the heads of a layer, each
+// with a matrix of its own): C_b[M, N] = A_b[M, K] * W_b[N, K]^T, b = 0 .. batch - 1.
+CCB_API int ccb_gemm_bf16_batched(void* handle, void* C, const void* A, const void* W, int M, int N, int K, int lda,
+                                  int ldw, int ldc, long long sa, long long sw, long long sc, int batch,
+                                  int out_dtype, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0 || lda < K || ldw < K || ldc < N) return CCB_REFUSE_SIZE;
+  if (out_dtype != CCB_F32 && out_dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
+  cublasHandle_t h = (cublasHandle_t)handle;
+  cublasStatus_t st = cublasSetStream(h, stream);
+  if (st != CUBLAS_STATUS_SUCCESS) return 1000 + (int)st;
+  const float alpha = 1.f, beta = 0.f;
+  st = cublasGemmStridedBatchedEx(h, CUBLAS_OP_T, CUBLAS_OP_N, N, M, K, &alpha, W, CUDA_R_16BF, ldw, sw, A,
+                                  CUDA_R_16BF, lda, sa, &beta, C, out_dtype == CCB_F32 ? CUDA_R_32F : CUDA_R_16BF,
+                                  ldc, sc, batch, CUBLAS_COMPUTE_32F, CUBLAS_GEMM_DEFAULT);
+  return st == CUBLAS_STATUS_SUCCESS ? 0 : 1000 + (int)st;
+}

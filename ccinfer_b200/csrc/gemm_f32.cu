@@ -15,8 +15,11 @@ constexpr int kTN = 8;
 template <int TM>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A, const float* __restrict__ W, int M, int N,
-                int K, int lda, int ldw, int ldc) {
+                int K, int lda, int ldw, int ldc, long long sa, long long sw, long long sc) {
   ccb::pdl_begin();
+  C += (size_t)blockIdx.z * sc;   // one product of a batch per grid plane (strides 0: a single product)
+  A += (size_t)blockIdx.z * sa;
+  W += (size_t)blockIdx.z * sw;
   constexpr int BM = 16 * TM;
   __shared__ __align__(16) float As[kBK][BM];
   __shared__ __align__(16) float Ws[kBK][kBN];
@@ -98,18 +101,29 @@ gemm_f32_kernel(float* __restrict__ C, const float* __restrict__ A, const float*
 
 // Zero padding of the k range adds exact zeros at the end of a chain, which
 // does not change a float sum, so ragged K is exact too.
+static int gemm_f32_launch(float* C, const float* A, const float* W, int M, int N, int K, int lda, int ldw, int ldc,
+                           long long sa, long long sw, long long sc, int batch, cudaStream_t stream) {
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (K <= 0 || lda < K || ldw < K || ldc < N || batch > 65535) return CCB_REFUSE_SIZE;
+  const int gx = (N + kBN - 1) / kBN;
+#define CCB_F32_GO(TM, BM) \
+  ccb_launch(gemm_f32_kernel<TM>, dim3(gx, (M + BM - 1) / BM, batch), 256, 0, stream, C, A, W, M, N, K, lda, ldw, \
+             ldc, sa, sw, sc)
+  if (M <= 16) CCB_F32_GO(1, 16);
+  else if (M <= 32) CCB_F32_GO(2, 32);
+  else if (M <= 64) CCB_F32_GO(4, 64);
+  else CCB_F32_GO(8, 128);
+#undef CCB_F32_GO
+  return ccb_launch_status();
+}
+
 CCB_API int ccb_gemm_f32(float* C, const float* A, const float* W, int M, int N, int K, int lda, int ldw, int ldc,
                          cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
-  if (K <= 0 || lda < K || ldw < K || ldc < N) return CCB_REFUSE_SIZE;
-  const int gx = (N + kBN - 1) / kBN;
-  if (M <= 16)
-    ccb_launch(gemm_f32_kernel<1>, dim3(gx, (M + 15) / 16), 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
-  else if (M <= 32)
-    ccb_launch(gemm_f32_kernel<2>, dim3(gx, (M + 31) / 32), 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
-  else if (M <= 64)
-    ccb_launch(gemm_f32_kernel<4>, dim3(gx, (M + 63) / 64), 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
-  else
-    ccb_launch(gemm_f32_kernel<8>, dim3(gx, (M + 127) / 128), 256, 0, stream, C, A, W, M, N, K, lda, ldw, ldc);
-  return ccb_launch_status();
+  return gemm_f32_launch(C, A, W, M, N, K, lda, ldw, ldc, 0, 0, 0, 1, stream);
+}
+
+// A batch of products of equal shapes at fixed strides (in elements): C_b = A_b W_b^T.
+CCB_API int ccb_gemm_f32_batched(float* C, const float* A, const float* W, int M, int N, int K, int lda, int ldw,
+                                 int ldc, long long sa, long long sw, long long sc, int batch, cudaStream_t stream) {
+  return gemm_f32_launch(C, A, W, M, N, K, lda, ldw, ldc, sa, sw, sc, batch, stream);
 }

@@ -413,3 +413,72 @@ CCB_API int ccb_postnorm_residual(void* y, float* h, const void* delta, const fl
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// Layer scale: h += delta * ls (one factor per channel), and in the same pass what reads the stream next:
+//   w_next given:   y = RMSNorm(h; w_next)
+//   else y given:   y = h in the storage type (the rows of a product that reads the stream itself)
+// delta and y in the storage type, h, ls and w_next float.  D a multiple of 4 with 16-byte rows: four channels a
+// thread and step; else one.
+template <typename T, bool VEC>
+__global__ void __launch_bounds__(kNormThreads)
+scaled_residual_kernel(T* __restrict__ y, float* __restrict__ h, const T* __restrict__ delta,
+                       const float* __restrict__ ls, const float* __restrict__ w_next, float eps_next, int D) {
+  ccb::pdl_begin();
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  float* hr = h + (size_t)r * D;
+  const T* dr = delta + (size_t)r * D;
+  T* yr = y ? y + (size_t)r * D : nullptr;
+  float ss = 0.f;
+  if (VEC) {
+    for (int i = threadIdx.x; i < (D >> 2); i += kNormThreads) {
+      float4 v = Vec4<float>::load(hr + 4 * i);
+      const float4 d = Vec4<T>::load(dr + 4 * i), s = Vec4<float>::load(ls + 4 * i);
+      v.x = fmaf(d.x, s.x, v.x); v.y = fmaf(d.y, s.y, v.y); v.z = fmaf(d.z, s.z, v.z); v.w = fmaf(d.w, s.w, v.w);
+      Vec4<float>::store(hr + 4 * i, v);
+      ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+      if (yr && !w_next) Vec4<T>::store(yr + 4 * i, v);
+    }
+  } else {
+    for (int d = threadIdx.x; d < D; d += kNormThreads) {
+      const float v = fmaf(to_f32(dr[d]), ls[d], hr[d]);
+      hr[d] = v;
+      ss += v * v;
+      if (yr && !w_next) yr[d] = from_f32<T>(v);
+    }
+  }
+  if (w_next == nullptr) return;
+  ss = block_sum<kNormThreads>(ss, red);   // (its barriers also make the block's writes of h visible to it)
+  const float inv = 1.0f / sqrtf(ss / (float)D + eps_next);
+  if (VEC) {
+    for (int i = threadIdx.x; i < (D >> 2); i += kNormThreads) {
+      const float4 v = Vec4<float>::load(hr + 4 * i), g = Vec4<float>::load(w_next + 4 * i);
+      Vec4<T>::store(yr + 4 * i, make_float4(v.x * inv * g.x, v.y * inv * g.y, v.z * inv * g.z, v.w * inv * g.w));
+    }
+  } else {
+    for (int d = threadIdx.x; d < D; d += kNormThreads) yr[d] = from_f32<T>(hr[d] * inv * w_next[d]);
+  }
+}
+
+CCB_API int ccb_scaled_residual(void* y, float* h, const void* delta, const float* ls, const float* w_next,
+                                float eps_next, int rows, int D, int dtype, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (D <= 0) return CCB_REFUSE_SIZE;
+  if (h == nullptr || delta == nullptr || ls == nullptr || (w_next != nullptr && y == nullptr)) return CCB_REFUSE_ARG;
+  const bool vec = (D % 4 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(h) | reinterpret_cast<uintptr_t>(delta) |
+                     reinterpret_cast<uintptr_t>(ls) | reinterpret_cast<uintptr_t>(w_next)) & 15) == 0;
+#define CCB_SCALED(TT, VV)                                                                                      \
+  ccb_launch(scaled_residual_kernel<TT, VV>, dim3(rows), dim3(kNormThreads), 0, stream, (TT*)y, h, (const TT*)delta, \
+             ls, w_next, eps_next, D)
+  if (dtype == CCB_F32) {
+    if (vec) CCB_SCALED(float, true); else CCB_SCALED(float, false);
+  } else if (dtype == CCB_BF16) {
+    if (vec) CCB_SCALED(__nv_bfloat16, true); else CCB_SCALED(__nv_bfloat16, false);
+  } else {
+    return CCB_REFUSE_DTYPE;
+  }
+#undef CCB_SCALED
+  return ccb_launch_status();
+}

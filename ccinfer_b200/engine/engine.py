@@ -414,23 +414,27 @@ class Engine:
 
     def _forward(self, step: StepContext) -> Optional[torch.Tensor]:
         plan = self.plan
-        if getattr(plan.embedding, "takes_first_norm", False) and plan.order:
+        if getattr(plan.embedding, "takes_first_norm", False) and plan.order and plan.order[0].enter is None:
             stream = plan.embedding.forward(step, getattr(plan.layers[plan.order[0].layer], "first_norm", None))
         else:
             stream = plan.embedding.forward(step)
         first_rows = None
-        if any(e.add_embedding for e in plan.order):
+        if any(e.add_embedding or e.enter is not None for e in plan.order):
             # a repeated pass starts from its input plus the embedding's rows: they are kept beside the stream
             first_rows = self.rt.scratch.get("embedding_rows", (self.rt.max_tokens, stream.h.shape[1]),
                                              torch.float32)[:step.n_tokens]
             first_rows.copy_(stream.h)
         for i, e in enumerate(plan.order):
             block = plan.layers[e.layer]
+            if e.enter is not None:   # the pass that begins here starts from a transform of the stream
+                e.enter.forward(stream, first_rows, e.enter_number, step)
             cache = None
             if i in self._entry_group:
                 src = i if e.cache_of is None else e.cache_of
                 cache = LayerCache(self._cache[src], step.groups[self._entry_group[i]], own=e.cache_of is None)
             nxt = plan.layers[plan.order[i + 1].layer] if i + 1 < len(plan.order) else None
+            if nxt is not None and plan.order[i + 1].enter is not None:
+                nxt = None   # the stream changes before the next block reads it: nobody writes its norm ahead
             stream.next_norm = getattr(nxt, "first_norm", None)
             stream.next_add = first_rows if nxt is not None and plan.order[i + 1].add_embedding else None
             block.forward(stream, step, cache, self._state.get(i))

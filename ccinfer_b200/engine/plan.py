@@ -16,11 +16,15 @@ class RunEntry:
     earlier entry of the order whose cache this run reads instead of keeping
     one (its mixer then writes no keys or values).  ``add_embedding``: before
     this run the embedding's rows are added to the stream once more (the first
-    layer of a repeated pass over some layers).
+    layer of a repeated pass over some layers).  ``enter``: a part whose ``forward(stream, embedding_rows,
+    enter_number, step)`` transforms the stream before this run (a pass that starts from a mix of its input and
+    the embedding's rows); it is one of ``ModelPlan.extras``.
     """
     layer: int
     cache_of: Optional[int] = None
     add_embedding: bool = False
+    enter: Optional[Part] = None
+    enter_number: int = 0
 
 
 @dataclasses.dataclass
@@ -32,9 +36,10 @@ class ModelPlan:
     head: Part               # forward(x_rows) -> float logits
     vocab_size: int
     max_position: Optional[int] = None
+    extras: List[Part] = dataclasses.field(default_factory=list)   # parts outside the layers (``RunEntry.enter``)
 
     def parts(self):
-        return [self.embedding] + list(self.layers) + [self.final_norm, self.head]
+        return [self.embedding] + list(self.layers) + list(self.extras) + [self.final_norm, self.head]
 
     def tensor_specs(self):
         """All tensors of the model, each name once (a tied head names the embedding's tensor again)."""
@@ -61,6 +66,10 @@ class ModelPlan:
                 raise ValueError(f"order[{i}] names layer {e.layer}, the model has {len(self.layers)}")
             if e.add_embedding and i == 0:
                 raise ValueError("order[0] cannot add the embedding's rows: the stream holds nothing else yet")
+            if e.enter is not None and not any(e.enter is x for x in self.extras):
+                raise ValueError(f"order[{i}] enters through a part that is not among the plan's extras")
+            if e.enter is not None and e.add_embedding:
+                raise ValueError(f"order[{i}]: a run either adds the embedding's rows or enters through a part")
             if e.cache_of is not None:
                 if not (0 <= e.cache_of < i):
                     raise ValueError(f"order[{i}] reads the cache of entry {e.cache_of}, which does not run before it")

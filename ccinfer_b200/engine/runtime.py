@@ -139,6 +139,15 @@ class Runtime:
         self.cublas.gemm_bf16(out, x, w)
         return out
 
+    def linear_batched(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+        """out[b] = x[b] @ w[b]^T for 3-d views [batch, M, *] (the heads of a layer, each with a matrix of its
+        own); rows and batches may be strided; out may be float for bfloat16 operands."""
+        if self.dtype == torch.float32:
+            kernels.gemm_f32_batched(out, x, w)
+        else:
+            self.cublas.gemm_bf16_batched(out, x, w)
+        return out
+
     def gated_up(self, act: torch.Tensor, x: torch.Tensor, w: torch.Tensor, block: int, activation=None) -> torch.Tensor:
         """act[M, F] = silu(x Wg^T) * (x Wu^T) for the merged weight w [2F, K] (``block``: see kernels.silu_mul).
 

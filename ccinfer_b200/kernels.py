@@ -75,7 +75,28 @@ _SIGNATURES = {
     "ccb_delta_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_gated_head_rmsnorm": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_float, c_int,
-                               c_void_p],
+                               c_int, c_void_p],
+    "ccb_gated_linear_recurrence": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_gla_prepare": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
+    "ccb_latent_prepare": [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                           c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "ccb_latent_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                             c_int, c_void_p, c_void_p],
+    "ccb_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                      c_void_p],
+    "ccb_moe_dense_act": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_scaled_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
+    "ccb_concat_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ccb_add_row": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "ccb_gelu_gate_rows": [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int,
+                           c_int, c_void_p, c_void_p],
+    "ccb_gemm_f32_batched": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_longlong,
+                             c_longlong, c_longlong, c_int, c_void_p],
+    "ccb_gemm_bf16_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                              c_longlong, c_longlong, c_longlong, c_int, c_int, c_void_p],
     "ccb_paged_attention_generic": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                     c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                                     c_void_p, c_void_p],
@@ -426,14 +447,150 @@ def delta_recurrence(qn, kn, vv, gg, bb, state, out, cu_q, state_slot, n_entries
                                       _p(state_slot), n_entries, G, H, dk, dv, _stream()), "delta_recurrence")
 
 
-def gated_head_rmsnorm(y, o, gate, w, H: int, dv: int, eps: float) -> None:
-    """y[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * sigmoid(gate[t, h, :]); o float, gate and y storage type."""
+def gated_head_rmsnorm(y, o, gate, w, H: int, dv: int, eps: float, silu_gate: bool = False) -> None:
+    """y[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w * sigmoid(gate[t, h, :]); o float, gate and y storage type.
+    ``silu_gate``: the factor is gate * sigmoid(gate) instead."""
     _cuda(y, o, w)
     T = y.shape[0]
     assert o.dtype == torch.float32 and w.dtype == torch.float32 and w.numel() == dv and gate.stride(1) == 1
     assert gate.dtype == y.dtype
     _check(lib().ccb_gated_head_rmsnorm(_p(y), _p(o), _p(gate), gate.stride(0), _p(w), T, H, dv, float(eps),
-                                        _dt(y), _stream()), "gated_head_rmsnorm")
+                                        1 if silu_gate else 0, _dt(y), _stream()), "gated_head_rmsnorm")
+
+
+def gated_linear_recurrence(qn, kn, vv, gg, state, out, cu_q, state_slot, n_entries: int, H: int, dk: int,
+                            dv: int) -> None:
+    """S <- diag(g_t) S + k_t v_t^T, out_t = S^T q_t over each request's tokens of the step, from and into
+    ``state`` [slots, H, dv, dk] (float); the rows float [T, H, dk] (q, k, g) and [T, H, dv] (v, out)."""
+    _cuda(qn, kn, vv, gg, state, out, cu_q, state_slot)
+    assert state.dtype == torch.float32 and state.shape[1:] == (H, dv, dk) and out.dtype == torch.float32
+    assert qn.dtype == kn.dtype == vv.dtype == gg.dtype == torch.float32
+    _check(lib().ccb_gated_linear_recurrence(_p(qn), _p(kn), _p(vv), _p(gg), _p(state), _p(out), _p(cu_q),
+                                             _p(state_slot), n_entries, H, H, dk, dv, _stream()),
+           "gated_linear_recurrence")
+
+
+def gla_prepare(proj, offsets, a, bias, qn, kn, vv, gg, H: int, dk: int, dv: int, q_mult: float, tau: float) -> None:
+    """The float rows of the gated linear recurrence from the projections' rows: q * q_mult, k, v, and the decay
+    sigmoid(a + bias)^(1 / tau) per head and key channel.  ``offsets``: first columns of q, k, v in ``proj``."""
+    _cuda(bias, qn, kn, vv, gg)
+    T = qn.shape[0]
+    assert proj.stride(1) == 1 and a.stride(1) == 1 and proj.dtype == a.dtype
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == H * dk)
+    oq, ok, ov = offsets
+    _check(lib().ccb_gla_prepare(_p(proj), proj.stride(0), oq, ok, ov, _p(a), a.stride(0), _p(bias), _p(qn), _p(kn),
+                                 _p(vv), _p(gg), T, H, dk, dv, float(q_mult), float(tau), _dt(proj), _stream()),
+           "gla_prepare")
+
+
+def latent_prepare(proj, oq: int, oc: int, w, inv_freq, rot_dims: int, positions, slot_map, cache, qa, H: int,
+                   d: int, r: int, R: int, eps: float, status=None) -> None:
+    """The cache rows and the rotated query parts of latent attention from the projections' rows.
+
+    ``proj`` [T, >=]: H query heads of [d | r] from column ``oq``, the latent row [R | r] from ``oc``.  Token t's
+    cache row (``cache`` viewed as [slots, R + r], slot_map[t]; a negative slot skips it) gets
+    [x / rms(x) * w | rot(x')]; ``qa`` float [T, H, R + r] gets rot(q's last r) in the last r places of each head.
+    The rotation turns the pairs (i, i + rot_dims / 2) of the first rot_dims coordinates by pos * inv_freq[i]."""
+    _cuda(w, inv_freq, positions, slot_map, cache, qa, status)
+    T = qa.shape[0]
+    assert proj.stride(1) == 1 and proj.dtype == cache.dtype and qa.dtype == torch.float32
+    assert qa.shape == (T, H, R + r) and w.dtype == torch.float32 and w.numel() == R
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() >= rot_dims // 2)
+    assert cache.shape[-1] == R + r
+    _check(lib().ccb_latent_prepare(_p(proj), proj.stride(0), oq, oc, _p(w), _p(inv_freq), rot_dims, _p(positions),
+                                    _p(slot_map), _p(cache), cache.numel() // (R + r), _p(qa), T, H, d, r, R,
+                                    float(eps), _dt(proj), _p(status), _stream()), "latent_prepare")
+
+
+def latent_attention(qa, cache, sink, gate, out, cu_q, pos0, entry_of_token, block_table, entry0: int, n_entries: int,
+                     max_q: int, page_size: int, window: int, scale: float, status=None) -> None:
+    """Attention of the step's entries entry0 .. entry0 + n_entries - 1 (none with more than ``max_q`` tokens) over
+    the cached rows [c | kr] (``cache`` [pages, page_size, R + r]): every head of ``qa`` float [T, H, R + r] reads
+    the same rows; a query at position p sees p - window + 1 .. p; the softmax has one more term exp(sink[h]);
+    out[t, h, :] = sigmoid(gate[t, h]) * sum_j p_j c_j, [T, H, R] in the storage type."""
+    _cuda(qa, cache, sink, out, cu_q, pos0, entry_of_token, block_table, status)
+    T, H, W = qa.shape
+    R = out.shape[2]
+    assert out.shape == (T, H, R) and cache.shape[1:] == (page_size, W) and out.dtype == cache.dtype == gate.dtype
+    assert sink.dtype == torch.float32 and sink.numel() == H and gate.stride(1) == 1 and qa.dtype == torch.float32
+    _check(lib().ccb_latent_attention(_p(qa), _p(cache), _p(sink), _p(gate), gate.stride(0), _p(out), _p(cu_q),
+                                      _p(pos0), _p(entry_of_token), _p(block_table), block_table.stride(0), entry0,
+                                      n_entries, max_q, H, R, W - R, page_size, cache.shape[0], int(window),
+                                      float(scale), _dt(out), _p(status), _stream()), "latent_attention")
+
+
+def moe_route(logits, correction, idx, wts, dense_w, groups: int, keep: int) -> None:
+    """The router's choice per token from float logits [T, E]: softmax scores, + ``correction`` for the choice,
+    only experts of the ``keep`` best of ``groups`` groups of neighbours, the top idx.shape[1] of them.
+    idx int32 [T, top], wts float [T, top] (the chosen experts' scores, not renormalised), dense_w (optional)
+    float [T, E]: the same weights as a dense row."""
+    _cuda(correction, idx, wts, dense_w)
+    T, E = logits.shape
+    top = idx.shape[1]
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and idx.dtype == torch.int32
+    assert idx.shape == (T, top) and wts.shape == (T, top) and wts.dtype == torch.float32 and idx.is_contiguous()
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    assert dense_w is None or (dense_w.dtype == torch.float32 and dense_w.shape == (T, E))
+    _check(lib().ccb_moe_route(_p(logits), logits.stride(0), _p(correction), _p(idx), _p(wts), _p(dense_w), T, E,
+                               int(groups), int(keep), top, _stream()), "moe_route")
+
+
+def moe_dense_act(act, dense_w, E: int, F: int, shared: int) -> None:
+    """In place on the rows of ONE product over all experts' first matrices: act[t, e * F + f] =
+    relu(act)^2 * dense_w[t, e]; the ``shared`` columns after the experts get relu(act)^2."""
+    _cuda(dense_w)
+    T = act.shape[0]
+    assert act.stride(1) == 1 and act.shape[1] == E * F + shared and dense_w.dtype == torch.float32
+    _check(lib().ccb_moe_dense_act(_p(act), act.stride(0), _p(dense_w), T, E, F, shared, _dt(act), _stream()),
+           "moe_dense_act")
+
+
+def scaled_residual(h, delta, ls, y=None, w_next=None, eps_next: float = 0.0) -> None:
+    """h += delta * ls (a factor per channel); with ``w_next`` y = RMSNorm(h; w_next), else with ``y`` y = h in
+    the storage type.  h, ls, w_next float; delta and y in the storage type."""
+    _cuda(h, delta, ls, y, w_next)
+    T, D = h.shape
+    assert h.dtype == torch.float32 and delta.shape == (T, D) and ls.dtype == torch.float32 and ls.numel() == D
+    assert y is None or (y.shape == (T, D) and y.dtype == delta.dtype)
+    assert w_next is None or (y is not None and w_next.dtype == torch.float32 and w_next.numel() == D)
+    _check(lib().ccb_scaled_residual(_p(y), _p(h), _p(delta), _p(ls), _p(w_next), float(eps_next), T, D, _dt(delta),
+                                     _stream()), "scaled_residual")
+
+
+def concat_cast(out, a, b) -> None:
+    """out[t, :] = [a[t, :] | b[t, :]] in the storage type; a, b float [T, D]."""
+    _cuda(out, a, b)
+    T, D = a.shape
+    assert a.dtype == b.dtype == torch.float32 and b.shape[1] == D and b.shape[0] >= T and out.shape == (T, 2 * D)
+    _check(lib().ccb_concat_cast(_p(out), _p(a), _p(b), T, D, _dt(out), _stream()), "concat_cast")
+
+
+def add_row(h, row) -> None:
+    """h[t, :] += row (float)."""
+    _cuda(h, row)
+    T, D = h.shape
+    assert h.dtype == row.dtype == torch.float32 and row.numel() == D
+    _check(lib().ccb_add_row(_p(h), _p(row), T, D, _stream()), "add_row")
+
+
+def gelu_gate_rows(g, table, off: int, ids, status=None, pending=None) -> None:
+    """g[t, j] = gelu_tanh(g[t, j]) * table[ids[t], off + j] in place (g [T, n], rows may be strided)."""
+    _cuda(table, ids, status, pending)
+    T, n = g.shape
+    assert g.stride(1) == 1 and g.dtype == table.dtype and ids.dtype == torch.int32 and ids.numel() >= T
+    _check(lib().ccb_gelu_gate_rows(_p(g), g.stride(0), _p(table), table.stride(0), int(off), _p(ids), T, n,
+                                    table.shape[0], _p(pending), 0 if pending is None else pending.numel(), _dt(g),
+                                    _p(status), _stream()), "gelu_gate_rows")
+
+
+def gemm_f32_batched(c, a, w) -> None:
+    """c[b] = a[b] @ w[b]^T for 3-d views [batch, M, *] in true 32-bit arithmetic; rows and batches may be strided."""
+    assert c.dtype == a.dtype == w.dtype == torch.float32
+    B, M, K = a.shape
+    N = w.shape[1]
+    assert w.shape == (B, N, K) and c.shape == (B, M, N) and a.stride(2) == w.stride(2) == c.stride(2) == 1
+    _check(lib().ccb_gemm_f32_batched(_p(c), _p(a), _p(w), M, N, K, a.stride(1), w.stride(1), c.stride(1),
+                                      a.stride(0), w.stride(0), c.stride(0), B, _stream()), "gemm_f32_batched")
 
 
 def paged_attention_generic(q, k_cache, v_cache, out, positions, entry_of_token, block_table, n_entries: int,
@@ -853,6 +1010,17 @@ class CublasHandle:
         assert w.shape[1] == K and c.shape == (M, N) and a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1
         _check(lib().ccb_gemm_bf16(self._h, _p(c), _p(a), _p(w), M, N, K, a.stride(0), w.stride(0), c.stride(0),
                                    _dt(c), _stream()), "gemm_bf16")
+
+    def gemm_bf16_batched(self, c, a, w) -> None:
+        """c[b] = a[b] @ w[b]^T for 3-d views [batch, M, *]: bfloat16 operands, float accumulation, c bfloat16 or
+        float; rows and batches may be strided."""
+        assert a.dtype == w.dtype == torch.bfloat16 and c.dtype in _DT
+        B, M, K = a.shape
+        N = w.shape[1]
+        assert w.shape == (B, N, K) and c.shape == (B, M, N) and a.stride(2) == w.stride(2) == c.stride(2) == 1
+        _check(lib().ccb_gemm_bf16_batched(self._h, _p(c), _p(a), _p(w), M, N, K, a.stride(1), w.stride(1),
+                                           c.stride(1), a.stride(0), w.stride(0), c.stride(0), B, _dt(c), _stream()),
+               "gemm_bf16")
 
     def close(self):
         if self._h:

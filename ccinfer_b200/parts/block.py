@@ -114,3 +114,86 @@ class SandwichNormBlock(Block):
             m = self.ffn.forward(x, step)
             x = self._sum(stream, m, self.post2, after, True)
         stream.ready = (after, x) if (after is not None and x is not None) else None
+
+
+class LayerScaleBlock(Block):
+    """Pre-norm with a factor per channel on each sublayer's output, and optionally a token side input last:
+
+        h += ls1 * Mixer(norm1(h));   h += ls2 * FeedForward(norm2(h));   h += side(h, token)
+
+    The feed-forward (with norm2 and ls2) may be absent.  Each sum is one kernel that also writes what reads the
+    stream next: the next norm's rows, or the stream's own rows in the compute type for the side input's gate.
+    The side input's sum (with its RMS norm) writes the first norm of the block that follows (``stream.ready``).
+    ``ls_names``: the tensors of ls1 and ls2."""
+
+    def __init__(self, dim: int, norm1, mixer: Mixer, ls_names, norm2=None, ffn: Optional[FeedForward] = None,
+                 side=None):
+        if (ffn is None) != (norm2 is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is given")
+        self.dim, self.norm1, self.mixer, self.norm2, self.ffn, self.side = int(dim), norm1, mixer, norm2, ffn, side
+        self.ls_names = tuple(ls_names)
+        self.rt = None
+
+    def _parts(self):
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn, self.side) if p is not None]
+
+    @property
+    def graph_safe(self):
+        return all(p.graph_safe for p in self._parts())
+
+    def tensor_specs(self):
+        from .base import TensorSpec
+        specs = [s for p in self._parts() for s in p.tensor_specs()]
+        n = 2 if self.ffn is not None else 1
+        return specs + [TensorSpec(name, (self.dim,), role="vector", init="one_plus_normal") for name in self.ls_names[:n]]
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+        for p in self._parts():
+            p.bind(rt, fetch)
+        self.ls1 = fetch(self.ls_names[0]).float().contiguous()
+        self.ls2 = fetch(self.ls_names[1]).float().contiguous() if self.ffn is not None else None
+
+    @property
+    def first_norm(self):
+        return self.norm1
+
+    def _rows_buffer(self, key, T):
+        rt = self.rt
+        return rt.scratch.get(key, (rt.max_tokens, self.dim), rt.dtype)[:T]
+
+    def _sum(self, stream, delta, ls, nxt, last: bool):
+        """h += ls * delta; returns the rows of what reads the stream next: ``nxt``'s (a norm with a weight and
+        an eps), the stream's own rows in the compute type before a side input, or None."""
+        rt = self.rt
+        T = stream.h.shape[0]
+        delta = rt.rows(delta)
+        if last and self.side is not None:
+            rows = self._rows_buffer("stream_rows", T)
+            kernels.scaled_residual(stream.h, delta, ls, y=rows)
+            return rows
+        if nxt is not None and hasattr(nxt, "w") and hasattr(nxt, "eps"):
+            y = self._rows_buffer(nxt.scratch_key, T)
+            kernels.scaled_residual(stream.h, delta, ls, y=y, w_next=nxt.w, eps_next=nxt.eps)
+            return y
+        kernels.scaled_residual(stream.h, delta, ls)
+        return None
+
+    def forward(self, stream: Residual, step, cache, state) -> None:
+        rt = self.rt
+        after = stream.next_norm
+        stream.takes_unscaled = False
+        x = self.norm1.fold(stream)
+        step.residual_sink = None
+        a = self.mixer.forward(x, step, cache, state)
+        x = self._sum(stream, a, self.ls1, self.norm2 if self.ffn is not None else after, self.ffn is None)
+        if self.ffn is not None:
+            m = self.ffn.forward(x, step)
+            x = self._sum(stream, m, self.ls2, after, True)
+        if self.side is not None:
+            y = self.side.forward(x, step)
+            usable = after is not None and hasattr(after, "w") and hasattr(after, "eps")
+            x = self._rows_buffer(after.scratch_key, stream.h.shape[0]) if usable else None
+            kernels.postnorm_residual(stream.h, rt.rows(y), self.side.w, 1.0, self.side.eps, y=x,
+                                      w_next=after.w if usable else None, eps_next=after.eps if usable else 0.0)
+        stream.ready = (after, x) if (after is not None and x is not None) else None

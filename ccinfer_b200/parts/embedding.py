@@ -47,6 +47,78 @@ class TokenEmbedding(Part):
         return stream
 
 
+class TokenSideInput(Part):
+    """A second, narrow embedding of the token that enters the stream after a layer, through a gate:
+
+        e = table[token, offset : offset + dim];  g = gelu_tanh(Wgate h) * e;  y = Wproj g
+        h += y / rms(y) * w_norm
+
+    ``forward(h_rows, step)`` returns y (the caller sums it into the stream with its norm); the table is one
+    tensor for all layers, each reading its own ``dim`` columns from ``offset``."""
+
+    def __init__(self, vocab: int, hidden: int, dim: int, offset: int, table_width: int, eps: float, names: dict):
+        """``names``: tensor names under the keys table, gate, proj, norm."""
+        self.vocab, self.hidden, self.dim, self.offset = int(vocab), int(hidden), int(dim), int(offset)
+        self.table_width, self.eps, self.names = int(table_width), float(eps), dict(names)
+        self.w = None     # the norm's weight: the block's last sum applies it
+        self.rt = None
+
+    def tensor_specs(self):
+        n = self.names
+        return [TensorSpec(n["table"], (self.vocab, self.table_width)), TensorSpec(n["gate"], (self.dim, self.hidden)),
+                TensorSpec(n["proj"], (self.hidden, self.dim)),
+                TensorSpec(n["norm"], (self.hidden,), role="vector", init="one_plus_normal")]
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+        n = self.names
+        self.table = fetch(n["table"])
+        self.w_gate, self.w_proj = fetch(n["gate"]), fetch(n["proj"])
+        self.w = fetch(n["norm"]).float().contiguous()
+
+    def forward(self, h_rows: torch.Tensor, step) -> torch.Tensor:
+        rt = self.rt
+        T = h_rows.shape[0]
+        g = rt.scratch.get("side_gate", (rt.max_tokens, self.dim), rt.dtype)[:T]
+        rt.linear(g, h_rows, self.w_gate)
+        kernels.gelu_gate_rows(g, self.table, self.offset, step.token_ids, status=rt.status,
+                               pending=getattr(step, "pending_tokens", None))
+        y = rt.scratch.get("side_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
+        return rt.linear(y, g, self.w_proj)
+
+
+class LoopInput(Part):
+    """What a repeated pass over some layers starts from: h <- Win [h | h0] + step[t], h0 the embedding's rows,
+    t the number of the pass (``Win`` [D, 2 D] with the stream's columns first, ``step`` [passes, D])."""
+
+    def __init__(self, hidden: int, passes: int, names: dict):
+        """``names``: tensor names under the keys in, step."""
+        self.hidden, self.passes, self.names = int(hidden), int(passes), dict(names)
+        self.rt = None
+
+    needs_embedding = True
+
+    def tensor_specs(self):
+        D = self.hidden
+        return [TensorSpec(self.names["in"], (D, 2 * D)), TensorSpec(self.names["step"], (self.passes, D), role="vector")]
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+        self.w_in = fetch(self.names["in"])
+        self.steps = fetch(self.names["step"]).float().contiguous()
+
+    def forward(self, stream: Residual, first_rows: torch.Tensor, number: int, step) -> None:
+        rt = self.rt
+        if stream.pending is not None:
+            raise RuntimeError("the stream still has a sum pending where a pass begins")
+        T, D = stream.h.shape
+        both = rt.scratch.get("loop_rows", (rt.max_tokens, 2 * D), rt.dtype)[:T]
+        kernels.concat_cast(both, stream.h, first_rows)
+        rt.linear(stream.h, both, self.w_in)      # the product's rows are the float stream itself
+        kernels.add_row(stream.h, self.steps[number])
+        stream.ready = stream.unscaled = None
+
+
 class OutputHead(Part):
     def __init__(self, hidden: int, vocab: int, weight_name: str):
         self.hidden, self.vocab, self.weight_name = int(hidden), int(vocab), weight_name

@@ -1,0 +1,82 @@
+"""Mixture of experts: small feed-forward layers of which every token uses a few.
+
+    z = Wr x (float);  s = softmax(z) over all experts;  choice score c = s + correction
+    the experts form ``groups`` equal groups of neighbours; only experts of the ``keep`` groups with the largest
+    best choice score can be chosen; the ``top`` largest c are chosen; their weights are their s, as they are
+    m = sum_chosen s_e * Wdown_e act(Wup_e x)  +  Wdown_s act(Wup_s x)      (a shared expert for every token)
+
+``activation`` "relu2": act(u) = relu(u)^2.  No biases.
+
+Every expert on every token is ONE product over all experts' first matrices (the shared expert's rows after
+them), an activation that multiplies each expert's columns by the token's weight for it (zero where it was not
+chosen), and ONE product with all second matrices side by side, which also adds the experts up.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..errors import Unsupported
+from .base import FeedForward, TensorSpec
+
+
+class MixtureOfExperts(FeedForward):
+    def __init__(self, hidden: int, experts: int, top: int, expert_ff: int, names: dict, groups: int = 1,
+                 keep: int = 1, shared_ff: int = 0, activation: str = "relu2"):
+        """``names``: "router", "correction" (optional), "up" and "down" with ``{e}`` for the expert's number,
+        "shared_up" / "shared_down" (with ``shared_ff`` > 0)."""
+        if activation != "relu2":
+            raise Unsupported(f"expert activation {activation!r}")
+        if experts % groups or not (0 < keep <= groups) or not (0 < top <= (experts // groups) * keep):
+            raise Unsupported(f"{experts} experts in {groups} groups of which {keep} are kept cannot give {top}")
+        self.hidden, self.E, self.top, self.F = int(hidden), int(experts), int(top), int(expert_ff)
+        self.groups, self.keep, self.SF = int(groups), int(keep), int(shared_ff)
+        self.names = dict(names)
+        self.width = self.E * self.F + self.SF
+        self.rt = None
+
+    def tensor_specs(self):
+        n, D = self.names, self.hidden
+        specs = [TensorSpec(n["router"], (self.E, D))]
+        if n.get("correction"):
+            specs.append(TensorSpec(n["correction"], (self.E,), role="vector"))
+        for e in range(self.E):
+            specs += [TensorSpec(n["up"].format(e=e), (self.F, D)), TensorSpec(n["down"].format(e=e), (D, self.F))]
+        if self.SF:
+            specs += [TensorSpec(n["shared_up"], (self.SF, D)), TensorSpec(n["shared_down"], (D, self.SF))]
+        return specs
+
+    def bind(self, rt, fetch):
+        self.rt = rt
+        n = self.names
+        self.w_router = fetch(n["router"])
+        self.correction = fetch(n["correction"]).float().contiguous() if n.get("correction") else None
+        ups = [fetch(n["up"].format(e=e)) for e in range(self.E)]
+        downs = [fetch(n["down"].format(e=e)) for e in range(self.E)]
+        if self.SF:
+            ups.append(fetch(n["shared_up"]))
+            downs.append(fetch(n["shared_down"]))
+        self.w_up = torch.cat(ups, dim=0).contiguous()        # [E F + SF, D]
+        self.w_down = torch.cat(downs, dim=1).contiguous()    # [D, E F + SF]
+
+    def route(self, x, T):
+        """idx int32 [T, top], wts float [T, top], dense float [T, E] for the rows of x."""
+        rt = self.rt
+        logits = rt.scratch.get("moe_logits", (rt.max_tokens, self.E), torch.float32)[:T]
+        rt.linear(logits, x, self.w_router)
+        idx = rt.scratch.get("moe_idx", (rt.max_tokens, self.top), torch.int32)[:T]
+        wts = rt.scratch.get("moe_wts", (rt.max_tokens, self.top), torch.float32)[:T]
+        dense = rt.scratch.get("moe_dense", (rt.max_tokens, self.E), torch.float32)[:T]
+        kernels.moe_route(logits, self.correction, idx, wts, dense, self.groups, self.keep)
+        return idx, wts, dense
+
+    def forward(self, x, step):
+        rt = self.rt
+        x = rt.rows(x)
+        T = x.shape[0]
+        _, _, dense = self.route(x, T)
+        act = rt.scratch.get("moe_act", (rt.max_tokens, self.width), rt.dtype)[:T]
+        rt.linear(act, x, self.w_up)
+        kernels.moe_dense_act(act, dense, self.E, self.F, self.SF)
+        out = rt.scratch.get("ffn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]
+        return rt.linear(out, act, self.w_down)

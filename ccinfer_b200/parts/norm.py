@@ -8,17 +8,23 @@ from .base import Norm, Residual, TensorSpec, UnscaledRows
 
 
 class RMSNorm(Norm):
-    def __init__(self, dim: int, eps: float, weight_name: str, scratch_key: str = "normed"):
+    def __init__(self, dim: int, eps: float, weight_name: str, scratch_key: str = "normed", weight_offset: float = 0.0):
+        """``weight_offset`` c: the stored weight lies around zero and the norm multiplies by (c + w); the sum is
+        made once, in float, when the weight is bound (exact for a bfloat16 w of ordinary size)."""
         self.dim, self.eps, self.weight_name, self.scratch_key = int(dim), float(eps), weight_name, scratch_key
+        self.weight_offset = float(weight_offset)
         self.w = None
         self.rt = None
 
     def tensor_specs(self):
-        return [TensorSpec(self.weight_name, (self.dim,), role="vector", init="one_plus_normal")]
+        return [TensorSpec(self.weight_name, (self.dim,), role="vector",
+                           init="normal" if self.weight_offset else "one_plus_normal")]
 
     def bind(self, rt, fetch):
         self.rt = rt
         self.w = fetch(self.weight_name)
+        if self.weight_offset:
+            self.w = (self.w.float() + self.weight_offset).contiguous()
 
     def fold(self, stream: Residual, rows=None, n_rows=None):
         rt = self.rt
