@@ -151,3 +151,324 @@ CCB_API int ccb_moe_dense_act(void* act, int ld, const float* dense_w, int rows,
     return CCB_REFUSE_DTYPE;
   return ccb_launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The sparse form: only the chosen experts run.  The (token, choice) pairs of a step are sorted by expert; the
+// rows of an expert are cut into tiles of BM rows and every tile is one block row of a grouped product:
+//
+//   moe_sort       one block: counts per expert, their prefix sums, the place of every pair among its expert's
+//                  rows (pair_pos), the token and weight of every sorted row, and the list of tiles
+//   moe_grouped    C[row, :] = A[src(row), :] W_e^T for the rows of every tile, W_e the tile's expert:
+//                  bfloat16 on mma.sync m16n8k16 with float sums.  Both operands go from global memory straight
+//                  into the fragments: a thread loads 8 neighbouring k of its rows with ONE 16-byte access and
+//                  uses them as two k-pairs of two products.  Which k a fragment's place stands for does not
+//                  matter as long as A and B agree, and they do: both load the same way.
+//                  Epilogues: relu(c)^2 * weight(row) in the compute type (the experts' first product), or
+//                  float (the second); moe_combine adds each token's rows up in the order of its choices.
+//   The float path has a plain FFMA kernel of the same shape.
+#include "mma_common.cuh"
+
+namespace {
+
+constexpr int kSortThreads = 1024;
+
+// idx, wts [pairs] (pairs = tokens * top).  Outputs: src_row [pairs] (token of a sorted row), row_w [pairs],
+// pair_pos [pairs] (sorted row of a pair), tile_e / tile_r0 / tile_n [max_tiles].
+__global__ void __launch_bounds__(kSortThreads)
+moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int pairs, int top, int E, int BM,
+                int max_tiles, int* __restrict__ src_row, float* __restrict__ row_w, int* __restrict__ pair_pos,
+                int* __restrict__ tile_e, int* __restrict__ tile_r0, int* __restrict__ tile_n) {
+  ccb::pdl_begin();
+  extern __shared__ int sm[];
+  int* counts = sm;             // [E]
+  int* offs = sm + E;           // [E + 1]
+  int* tstart = offs + E + 1;   // [E + 1]
+  int* cursor = tstart + E + 1; // [E]
+  for (int e = threadIdx.x; e < E; e += kSortThreads) counts[e] = 0, cursor[e] = 0;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += kSortThreads) {
+    const int e = idx[p];
+    if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int o = 0, t = 0;
+    for (int e = 0; e < E; ++e) {
+      offs[e] = o;
+      tstart[e] = t;
+      o += counts[e];
+      t += (counts[e] + BM - 1) / BM;
+    }
+    offs[E] = o;
+    tstart[E] = t;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += kSortThreads) {
+    const int e = idx[p];
+    if (e < 0 || e >= E) { pair_pos[p] = -1; continue; }
+    const int pos = offs[e] + atomicAdd(&cursor[e], 1);
+    src_row[pos] = p / top;
+    row_w[pos] = wts[p];
+    pair_pos[p] = pos;
+  }
+  for (int t = threadIdx.x; t < max_tiles; t += kSortThreads) {
+    int n = 0, e = 0, r0 = 0;
+    if (t < tstart[E]) {
+      int lo = 0, hi = E - 1;   // the last expert whose first tile is <= t and that has tiles
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (tstart[mid] <= t) lo = mid; else hi = mid - 1;
+      }
+      e = lo;
+      const int j = t - tstart[e];
+      r0 = offs[e] + j * BM;
+      n = min(BM, counts[e] - j * BM);
+    }
+    tile_e[t] = e;
+    tile_r0[t] = r0;
+    tile_n[t] = n;
+  }
+}
+
+__device__ __forceinline__ uint4 ld16_or_zero(const __nv_bfloat16* p, bool ok) {
+  return ok ? *reinterpret_cast<const uint4*>(p) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// MODE 0: C (compute type) = relu(c)^2 * row_w[row];  MODE 1: C (float) = c.
+// A [*, lda]: row src_row[r] (MODE 0) or r itself (src_row null).  W_e = W + e * w_expert_stride, rows at ldw.
+template <int MT, int NT, int MODE>
+__global__ void __launch_bounds__(128)
+moe_grouped_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ src_row,
+                        const __nv_bfloat16* __restrict__ W, int ldw, long long w_expert_stride,
+                        void* __restrict__ Cout, int ldc, const float* __restrict__ row_w,
+                        const int* __restrict__ tile_e, const int* __restrict__ tile_r0,
+                        const int* __restrict__ tile_n, int N, int K) {
+  ccb::pdl_begin();
+  const int tile = blockIdx.x;
+  const int n_rows = tile_n[tile];
+  if (n_rows <= 0) return;
+  const int e = tile_e[tile], r0 = tile_r0[tile];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int n_base = (blockIdx.y * 4 + warp) * (8 * NT);
+  if (n_base >= N) return;
+  const __nv_bfloat16* We = W + (size_t)e * w_expert_stride;
+
+  const __nv_bfloat16* arow[MT][2];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      int r = m * 16 + hh * 8 + gid;
+      if (r >= n_rows) r = n_rows - 1;   // a row of the tile anyway; its result is not stored
+      const int g = r0 + r;
+      arow[m][hh] = A + (size_t)(src_row ? src_row[g] : g) * lda;
+    }
+  const __nv_bfloat16* wrow[NT];
+  bool wok[NT];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    const int col = n_base + n * 8 + gid;
+    wok[n] = col < N;
+    wrow[n] = We + (size_t)(wok[n] ? col : 0) * ldw;
+  }
+  float acc[MT][NT][4];
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int n = 0; n < NT; ++n)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
+
+  uint4 a[MT][2], b[NT];
+  auto load = [&](int k0) {
+    const int k = k0 + 8 * tig;
+    const bool ok = k < K;
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      a[m][0] = ld16_or_zero(arow[m][0] + k, ok);
+      a[m][1] = ld16_or_zero(arow[m][1] + k, ok);
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) b[n] = ld16_or_zero(wrow[n] + k, ok && wok[n]);
+  };
+  load(0);
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    uint4 ca[MT][2], cb[NT];
+#pragma unroll
+    for (int m = 0; m < MT; ++m) ca[m][0] = a[m][0], ca[m][1] = a[m][1];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) cb[n] = b[n];
+    if (k0 + 32 < K) load(k0 + 32);   // the next step's operands are on their way during this step's products
+#pragma unroll
+    for (int m = 0; m < MT; ++m) {
+      const uint32_t f0[4] = {ca[m][0].x, ca[m][1].x, ca[m][0].y, ca[m][1].y};
+      const uint32_t f1[4] = {ca[m][0].z, ca[m][1].z, ca[m][0].w, ca[m][1].w};
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        mma_bf16_16816(acc[m][n], f0, cb[n].x, cb[n].y);
+        mma_bf16_16816(acc[m][n], f1, cb[n].z, cb[n].w);
+      }
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < MT; ++m)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = m * 16 + hh * 8 + gid;
+      if (r >= n_rows) continue;
+      const size_t g = (size_t)(r0 + r);
+      const float wr = MODE == 0 ? row_w[g] : 1.f;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int col = n_base + n * 8 + 2 * tig;
+        float v0 = acc[m][n][hh * 2], v1 = acc[m][n][hh * 2 + 1];
+        if (MODE == 0) {
+          v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f);
+          v0 = v0 * v0 * wr; v1 = v1 * v1 * wr;
+          __nv_bfloat16* c = (__nv_bfloat16*)Cout + g * ldc + col;
+          if (col < N) c[0] = __float2bfloat16_rn(v0);
+          if (col + 1 < N) c[1] = __float2bfloat16_rn(v1);
+        } else {
+          float* c = (float*)Cout + g * ldc + col;
+          if (col < N) c[0] = v0;
+          if (col + 1 < N) c[1] = v1;
+        }
+      }
+    }
+}
+
+// The float path: a tile of up to 16 rows x 128 columns a block, a column a thread, A staged in shared memory.
+template <int MODE>
+__global__ void __launch_bounds__(128)
+moe_grouped_f32_kernel(const float* __restrict__ A, int lda, const int* __restrict__ src_row,
+                       const float* __restrict__ W, int ldw, long long w_expert_stride, float* __restrict__ C, int ldc,
+                       const float* __restrict__ row_w, const int* __restrict__ tile_e,
+                       const int* __restrict__ tile_r0, const int* __restrict__ tile_n, int N, int K) {
+  ccb::pdl_begin();
+  constexpr int KC = 32;
+  __shared__ float As[16][KC];
+  const int tile = blockIdx.x;
+  const int n_rows = tile_n[tile];
+  if (n_rows <= 0) return;
+  const int e = tile_e[tile], r0 = tile_r0[tile];
+  const int col = blockIdx.y * 128 + threadIdx.x;
+  const float* wr = W + (size_t)e * w_expert_stride + (size_t)(col < N ? col : 0) * ldw;
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += KC) {
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * KC; i += 128) {
+      const int r = i / KC, k = k0 + i % KC;
+      float v = 0.f;
+      if (r < n_rows && k < K) {
+        const int g = r0 + r;
+        v = A[(size_t)(src_row ? src_row[g] : g) * lda + k];
+      }
+      As[r][i % KC] = v;
+    }
+    __syncthreads();
+    const int kn = min(KC, K - k0);
+    for (int k = 0; k < kn; ++k) {
+      const float w = wr[k0 + k];
+#pragma unroll
+      for (int r = 0; r < 16; ++r) acc[r] = fmaf(As[r][k], w, acc[r]);
+    }
+  }
+  if (col >= N) return;
+  for (int r = 0; r < n_rows; ++r) {
+    float v = acc[r];
+    if (MODE == 0) {
+      v = fmaxf(v, 0.f);
+      v = v * v * row_w[r0 + r];
+    }
+    C[(size_t)(r0 + r) * ldc + col] = v;
+  }
+}
+
+// out[t, :] = (shared ? shared[t, :] : 0) + sum_k rows[pair_pos[t * top + k], :]   (float sums, fixed order)
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(T* __restrict__ out, const float* __restrict__ rows, const int* __restrict__ pair_pos,
+                   const T* __restrict__ shared, int top, int D, size_t total) {
+  ccb::pdl_begin();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / D;
+    const int c = (int)(i - t * D);
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int pos = pair_pos[t * top + k];
+      if (pos >= 0) v += rows[(size_t)pos * D + c];
+    }
+    if (shared) v += to_f32(shared[i]);
+    out[i] = from_f32<T>(v);
+  }
+}
+
+}  // namespace
+
+CCB_API int ccb_moe_sort(const int* idx, const float* wts, int pairs, int top, int E, int BM, int max_tiles,
+                         int* src_row, float* row_w, int* pair_pos, int* tile_e, int* tile_r0, int* tile_n,
+                         cudaStream_t stream) {
+  if (pairs <= 0) return 0;
+  if (E <= 0 || top <= 0 || BM <= 0 || max_tiles < (pairs + BM - 1) / BM + E) return CCB_REFUSE_SIZE;
+  const size_t smem = (size_t)(4 * E + 2) * sizeof(int);
+  if (smem > 96 * 1024) return CCB_REFUSE_SIZE;
+  cudaFuncSetAttribute(moe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  ccb_launch(moe_sort_kernel, dim3(1), dim3(kSortThreads), smem, stream, idx, wts, pairs, top, E, BM, max_tiles,
+             src_row, row_w, pair_pos, tile_e, tile_r0, tile_n);
+  return ccb_launch_status();
+}
+
+// mode 0: C (the compute type) [sorted rows, N] = relu(A[src_row] W_e^T)^2 * row_w;  mode 1: C (float) = A W_e^T
+// with A's rows the sorted rows themselves.  BM must be what moe_sort was given: 16, 32 or 64 (bfloat16), 16 (float).
+CCB_API int ccb_moe_grouped(const void* A, int lda, const int* src_row, const void* W, int ldw,
+                            long long w_expert_stride, void* C, int ldc, const float* row_w, const int* tile_e,
+                            const int* tile_r0, const int* tile_n, int max_tiles, int N, int K, int BM, int mode,
+                            int dtype, cudaStream_t stream) {
+  if (max_tiles <= 0 || N <= 0) return 0;
+  if (K <= 0 || (mode != 0 && mode != 1)) return CCB_REFUSE_SIZE;
+  if (dtype == CCB_F32) {
+    if (BM != 16) return CCB_REFUSE_SIZE;
+    dim3 grid(max_tiles, (N + 127) / 128);
+    if (mode == 0)
+      ccb_launch(moe_grouped_f32_kernel<0>, grid, dim3(128), 0, stream, (const float*)A, lda, src_row, (const float*)W,
+                 ldw, w_expert_stride, (float*)C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
+    else
+      ccb_launch(moe_grouped_f32_kernel<1>, grid, dim3(128), 0, stream, (const float*)A, lda, src_row, (const float*)W,
+                 ldw, w_expert_stride, (float*)C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
+    return ccb_launch_status();
+  }
+  if (dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
+  if (K % 8 || lda % 8 || ldw % 8 || w_expert_stride % 8 || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(W) & 15))
+    return CCB_REFUSE_SIZE;
+  dim3 grid(max_tiles, (N + 127) / 128);
+#define CCB_GROUPED(MT, MODE)                                                                                     \
+  ccb_launch(moe_grouped_bf16_kernel<MT, 4, MODE>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row, \
+             (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K)
+  if (BM == 16) { if (mode == 0) CCB_GROUPED(1, 0); else CCB_GROUPED(1, 1); }
+  else if (BM == 32) { if (mode == 0) CCB_GROUPED(2, 0); else CCB_GROUPED(2, 1); }
+  else if (BM == 64) { if (mode == 0) CCB_GROUPED(4, 0); else CCB_GROUPED(4, 1); }
+  else return CCB_REFUSE_SIZE;
+#undef CCB_GROUPED
+  return ccb_launch_status();
+}
+
+CCB_API int ccb_moe_combine(void* out, const float* rows, const int* pair_pos, const void* shared, int tokens, int top,
+                            int D, int dtype, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (top <= 0 || D <= 0) return CCB_REFUSE_SIZE;
+  const size_t total = (size_t)tokens * D;
+  const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
+  if (dtype == CCB_F32)
+    ccb_launch(moe_combine_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)out, rows, pair_pos,
+               (const float*)shared, top, D, total);
+  else if (dtype == CCB_BF16)
+    ccb_launch(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)out, rows,
+               pair_pos, (const __nv_bfloat16*)shared, top, D, total);
+  else
+    return CCB_REFUSE_DTYPE;
+  return ccb_launch_status();
+}
