@@ -88,6 +88,11 @@ _SIGNATURES = {
     "ccb_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                       c_void_p],
     "ccb_moe_dense_act": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_moe_sort": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                     c_void_p, c_void_p, c_void_p],
+    "ccb_moe_grouped": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
+                        c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_scaled_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
     "ccb_concat_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "ccb_add_row": [c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -543,6 +548,57 @@ def moe_dense_act(act, dense_w, E: int, F: int, shared: int) -> None:
     assert act.stride(1) == 1 and act.shape[1] == E * F + shared and dense_w.dtype == torch.float32
     _check(lib().ccb_moe_dense_act(_p(act), act.stride(0), _p(dense_w), T, E, F, shared, _dt(act), _stream()),
            "moe_dense_act")
+
+
+def moe_max_tiles(pairs: int, E: int, BM: int) -> int:
+    """Tiles of BM rows that the sorted (token, choice) pairs of a step can need at most."""
+    return -(-pairs // BM) + E
+
+
+def moe_sort(idx, wts, E: int, BM: int, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n) -> None:
+    """Sorts the (token, choice) pairs of ``idx`` / ``wts`` [T, top] by expert: pair_pos [T * top] = the sorted
+    row of every pair, src_row / row_w = token and weight of every sorted row, tile_* = the tiles of BM rows
+    that the experts' rows are cut into (tile_n = 0 for the unused tail of the list)."""
+    _cuda(idx, wts, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n)
+    T, top = idx.shape
+    n_tiles = tile_e.numel()
+    assert idx.dtype == torch.int32 and wts.dtype == torch.float32 and wts.shape == (T, top)
+    assert src_row.numel() >= T * top and row_w.numel() >= T * top and pair_pos.numel() >= T * top
+    assert tile_r0.numel() >= n_tiles and tile_n.numel() >= n_tiles and n_tiles >= moe_max_tiles(T * top, E, BM)
+    _check(lib().ccb_moe_sort(_p(idx), _p(wts), T * top, top, E, BM, n_tiles, _p(src_row), _p(row_w), _p(pair_pos),
+                              _p(tile_e), _p(tile_r0), _p(tile_n), _stream()), "moe_sort")
+
+
+def moe_grouped(c, a, src_row, w, w_expert_stride: int, row_w, tile_e, tile_r0, tile_n, N: int, K: int, BM: int,
+                mode: int) -> None:
+    """The product of every tile's rows with its expert's matrix (``w`` [*, ldw] viewed from the first expert's
+    first element, expert e at + e * w_expert_stride elements, N rows of K).  mode 0: c[row] = relu(a[src_row[row]]
+    W_e^T)^2 * row_w[row] in the compute type; mode 1: c[row] = a[row] W_e^T in float."""
+    _cuda(src_row, row_w, tile_e, tile_r0, tile_n)
+    assert a.stride(1) == 1 and w.stride(1) == 1 and c.stride(1) == 1 and a.dtype == w.dtype
+    assert c.dtype == (a.dtype if mode == 0 else torch.float32) and c.shape[1] == N and a.shape[1] == K
+    _check(lib().ccb_moe_grouped(_p(a), a.stride(0), _p(src_row), _p(w), w.stride(0), int(w_expert_stride), _p(c),
+                                 c.stride(0), _p(row_w), _p(tile_e), _p(tile_r0), _p(tile_n), tile_e.numel(), N, K, BM,
+                                 mode, _dt(a), _stream()), "moe_grouped")
+
+
+def moe_grouped_fits(dtype, K1: int, K2: int, *tensors) -> bool:
+    """Whether the grouped products take these operands: float always; bfloat16 with 16-byte rows."""
+    if dtype == torch.float32:
+        return True
+    return (K1 % 8 == 0 and K2 % 8 == 0
+            and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in tensors))
+
+
+def moe_combine(out, rows, pair_pos, shared, top: int) -> None:
+    """out[t] = (shared[t]) + sum over the token's choices k of rows[pair_pos[t * top + k]] (float sums in the
+    order of the choices); rows float [pairs, D], out and shared [T, D] in the compute type."""
+    _cuda(out, rows, pair_pos, shared)
+    T, D = out.shape
+    assert rows.dtype == torch.float32 and rows.shape[1] == D and pair_pos.dtype == torch.int32
+    assert shared is None or (shared.shape == (T, D) and shared.dtype == out.dtype)
+    _check(lib().ccb_moe_combine(_p(out), _p(rows), _p(pair_pos), _p(shared), T, top, D, _dt(out), _stream()),
+           "moe_combine")
 
 
 def scaled_residual(h, delta, ls, y=None, w_next=None, eps_next: float = 0.0) -> None:

@@ -7,9 +7,18 @@
 
 ``activation`` "relu2": act(u) = relu(u)^2.  No biases.
 
-Every expert on every token is ONE product over all experts' first matrices (the shared expert's rows after
-them), an activation that multiplies each expert's columns by the token's weight for it (zero where it was not
-chosen), and ONE product with all second matrices side by side, which also adds the experts up.
+Two forms, chosen by size (``sparse=`` forces one):
+
+* dense, for experts so small that launches cost more than their arithmetic: every expert on every token as ONE
+  product over all experts' first matrices (the shared expert's rows after them), an activation that multiplies
+  each expert's columns by the token's weight for it (zero where it was not chosen), and ONE product with all
+  second matrices side by side, which also adds the experts up;
+* sparse: the (token, choice) pairs are sorted by expert and only the chosen experts run, as two grouped
+  products over tiles of one expert's rows (``csrc/moe.cu``); the shared expert is two ordinary products; a last
+  kernel adds each token's rows up in the order of its choices.  A decode step then reads the chosen experts'
+  weights and no others.
+
+Both forms use the same merged weight tensors.
 """
 from __future__ import annotations
 
@@ -21,8 +30,12 @@ from .base import FeedForward, TensorSpec
 
 
 class MixtureOfExperts(FeedForward):
+    # from this many weights of the routed experts on, the sparse form runs (measured on B200: below, the dense
+    # form's two products cost less than the sparse form's extra launches)
+    SPARSE_MIN_WEIGHTS = 1 << 22
+
     def __init__(self, hidden: int, experts: int, top: int, expert_ff: int, names: dict, groups: int = 1,
-                 keep: int = 1, shared_ff: int = 0, activation: str = "relu2"):
+                 keep: int = 1, shared_ff: int = 0, activation: str = "relu2", sparse=None):
         """``names``: "router", "correction" (optional), "up" and "down" with ``{e}`` for the expert's number,
         "shared_up" / "shared_down" (with ``shared_ff`` > 0)."""
         if activation != "relu2":
@@ -33,6 +46,7 @@ class MixtureOfExperts(FeedForward):
         self.groups, self.keep, self.SF = int(groups), int(keep), int(shared_ff)
         self.names = dict(names)
         self.width = self.E * self.F + self.SF
+        self.sparse = sparse
         self.rt = None
 
     def tensor_specs(self):
@@ -70,10 +84,48 @@ class MixtureOfExperts(FeedForward):
         kernels.moe_route(logits, self.correction, idx, wts, dense, self.groups, self.keep)
         return idx, wts, dense
 
+    def _use_sparse(self, x) -> bool:
+        fits = kernels.moe_grouped_fits(self.rt.dtype, self.hidden, self.F, x, self.w_up, self.w_down)
+        if self.sparse is not None:
+            return bool(self.sparse) and fits
+        return fits and 2 * self.E * self.F * self.hidden >= self.SPARSE_MIN_WEIGHTS
+
+    def _forward_sparse(self, x, T):
+        rt = self.rt
+        E, F, D, top = self.E, self.F, self.hidden, self.top
+        i32, f32 = torch.int32, torch.float32
+        idx, wts, _ = self.route(x, T)
+        pairs, max_pairs = T * top, rt.max_tokens * top
+        # rows per tile: as many as an expert gets on average, so that its weights are read once per 16 to 64 rows
+        BM = 16 if (rt.dtype == f32 or pairs <= 16 * E) else (32 if pairs <= 32 * E else 64)
+        n_tiles = kernels.moe_max_tiles(pairs, E, BM)
+        cap = kernels.moe_max_tiles(max_pairs, E, 16)
+        src_row = rt.scratch.get("moe_src_row", (max_pairs,), i32)
+        row_w = rt.scratch.get("moe_row_w", (max_pairs,), f32)
+        pair_pos = rt.scratch.get("moe_pair_pos", (max_pairs,), i32)
+        tiles = [rt.scratch.get(f"moe_tile{k}", (cap,), i32)[:n_tiles] for k in range(3)]
+        kernels.moe_sort(idx, wts, E, BM, src_row, row_w, pair_pos, *tiles)
+        act = rt.scratch.get("moe_act_rows", (max_pairs, F), rt.dtype)[:pairs]
+        kernels.moe_grouped(act, x, src_row, self.w_up, F * self.w_up.stride(0), row_w, *tiles, F, D, BM, 0)
+        rows = rt.scratch.get("moe_out_rows", (max_pairs, D), f32)[:pairs]
+        kernels.moe_grouped(rows, act, None, self.w_down, F, row_w, *tiles, D, F, BM, 1)
+        shared = None
+        if self.SF:
+            sa = rt.scratch.get("moe_shared_act", (rt.max_tokens, self.SF), rt.dtype)[:T]
+            rt.linear(sa, x, self.w_up[E * F:])
+            kernels.moe_dense_act(sa, wts, 0, 1, self.SF)
+            shared = rt.scratch.get("moe_shared_out", (rt.max_tokens, D), rt.dtype)[:T]
+            rt.linear(shared, sa, self.w_down[:, E * F:])
+        out = rt.scratch.get("ffn_out", (rt.max_tokens, D), rt.dtype)[:T]
+        kernels.moe_combine(out, rows, pair_pos, shared, top)
+        return out
+
     def forward(self, x, step):
         rt = self.rt
         x = rt.rows(x)
         T = x.shape[0]
+        if self._use_sparse(x):
+            return self._forward_sparse(x, T)
         _, _, dense = self.route(x, T)
         act = rt.scratch.get("moe_act", (rt.max_tokens, self.width), rt.dtype)[:T]
         rt.linear(act, x, self.w_up)

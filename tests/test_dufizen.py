@@ -201,6 +201,41 @@ def test_router_kernel(E, groups, keep, top):
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sparse", [False, True])
+@pytest.mark.parametrize("E,top,F,D,groups,SF", [(8, 2, 64, 64, (4, 2), 32), (16, 4, 32, 128, None, 0), (5, 5, 8, 40, None, 8)])
+def test_mixture_of_experts_alone(dtype, sparse, E, top, F, D, groups, SF):
+    """The part by itself, in both of its forms, from one token to so many that an expert's rows fill several
+    tiles of every size."""
+    from ccinfer_b200.engine.runtime import Runtime
+    from ccinfer_b200.parts import MixtureOfExperts
+    rt = Runtime("cuda:0", dtype, 640, 4)
+    m = plain.moe_cfg(E, top, F, groups=groups, shared=SF or None)
+    g = torch.Generator().manual_seed(E + F)
+    W = {"router": 3 * torch.randn(E, D, generator=g) / math.sqrt(D), "correction": 0.1 * torch.randn(E, generator=g) - 0.05}
+    for e in range(E):
+        W[f"e{e}.up"] = torch.randn(F, D, generator=g) / math.sqrt(D)
+        W[f"e{e}.down"] = torch.randn(D, F, generator=g) / math.sqrt(F)
+    if SF:
+        W["shared.up"], W["shared.down"] = torch.randn(SF, D, generator=g) / math.sqrt(D), torch.randn(D, SF, generator=g) / math.sqrt(SF)
+    W = {k: v.to(torch.bfloat16).float() for k, v in W.items()}
+    names = {"router": "router", "correction": "correction", "up": "e{e}.up", "down": "e{e}.down",
+             "shared_up": "shared.up", "shared_down": "shared.down"}
+    part = MixtureOfExperts(D, E, top, F, names, *(groups or (1, 1)), SF, sparse=sparse)
+    part.bind(rt, lambda n: W[n].cuda().to(dtype) if W[n].dim() == 2 else W[n].cuda())
+    assert part._use_sparse(torch.empty(1, D, dtype=dtype, device="cuda")) == sparse
+    for T in (1, 5, 70, 300, 640):
+        x = torch.randn(T, D, generator=g).to(torch.bfloat16)
+        want = plain.moe(x.double(), {k: v.double() for k, v in W.items()}, "", m)
+        got = part.forward(x.cuda().to(dtype), None).double().cpu()
+        err = (got - want).abs().amax(-1) / want.abs().max()
+        tol = 2e-6 if dtype == torch.float32 else 1.5e-2
+        # (in bfloat16 a router's close call may go the other way for a token or two)
+        assert (err > tol).sum() <= (0 if dtype == torch.float32 else max(1, T // 50)), (T, err.max())
+    rt.check_status()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_batched_products(dtype):
     """A product per head over strided views (rows and heads at strides that are multiples of nothing)."""
     from ccinfer_b200.engine.runtime import Runtime
@@ -356,6 +391,26 @@ def test_replay_matches_plain(models, name, dtype, mode):
     print(f"[worst] {name}, {dtype}, {mode}: {worst:.3e}")
     eng.cache.check_consistency()
     assert all(p.used_pages == 0 for p in eng.cache.pools)
+
+
+@gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(plain.CONFIGS))
+def test_replay_with_the_sparse_experts(models, name, dtype, monkeypatch):
+    """The same models with the form of the mixture that runs only the chosen experts (which by itself starts at
+    sizes far above these), mixed batches and graphs."""
+    from ccinfer_b200.parts import MixtureOfExperts
+    monkeypatch.setattr(MixtureOfExperts, "SPARSE_MIN_WEIGHTS", 0)
+    calls = []
+    inner = MixtureOfExperts._forward_sparse
+    monkeypatch.setattr(MixtureOfExperts, "_forward_sparse", lambda self, x, T: (calls.append(T), inner(self, x, T))[1])
+    d, cfg, w, reqs, ref, page = models[name, dtype]
+    for steps, graphs in ((helpers.trace_whole(reqs), False), (helpers.trace_mixed(reqs, max_live=4, seed=7), True)):
+        pool = helpers.max_live_tokens(steps, round_to=max(64, page))
+        eng = engine_of(d, dtype, page, pool, max_requests=4, use_graphs=graphs)
+        rows = helpers.replay(eng, steps)
+        compare(rows, ref, dtype, f"{name} {dtype} sparse experts")
+    assert calls or (name == "B" and dtype == "bfloat16")   # (rows of 100 bfloat16 values are no 16-byte rows)
 
 
 @gpu
