@@ -35,9 +35,10 @@ runs one of the two other workloads of the reference's benchmark record through 
 continuous batch at the Qwen3-14B shape; four 16,384-token prompts at the Qwen3-32B shape) and prints a
 line of its own: output tokens a second, the distribution of the step calls, the pages' high water.
 
-    python bench.py --design tugelorn [--design-sizes mid,8b] [--layers L] [--design-profile]
+    python bench.py --design tugelorn|dufizen [--design-sizes mid,8b] [--layers L] [--design-profile]
 
-measures another design of the package beside Qwen3 at equal layer sizes (same width, heads, head size,
+measures another design of the package beside its closest model (Tugelorn beside Qwen3, Dufizen beside
+Tugelorn) at equal layer sizes (same width, heads, head size,
 intermediate size, vocabulary and number of layers; random weights): one prompt of 2,048 and of 8,192 tokens
 in steps of 2,048 (tokens a second) and decode steps of 1 and 8 requests after 2,048-token prompts, replayed
 from CUDA graphs (tokens a second), one JSON line per size.  With --design-profile it only runs a prompt and a
@@ -293,6 +294,28 @@ def tugelorn_config(size: str, layers: int):
     return TugelornConfig.from_json(j)
 
 
+def dufizen_config(size: str, layers: int):
+    """Layers in turn: latent attention over a window (heads of head size - 64 unrotated + 64 rotated coordinates,
+    latent size 512), gated linear attention; each with a mixture of 32 experts of which 4 are used plus a shared
+    one (4 * F / 8 + F / 2 = F intermediate channels per token, as a dense feed-forward of F); a token side input of
+    256 columns; the two middle layers are a loop of one pass (they enter through the loop's product)."""
+    from ccinfer_b200.config.dufizen import DufizenConfig
+    D, H, G, hd, F, V = DESIGN_SIZES[size]
+    kinds = [
+        {"type": "latent_attention", "mixer": {"heads": H, "dim": hd - 64, "rot_dim": 64, "vdim": hd, "kv_rank": 512,
+                                               "scale": hd ** -0.5, "mask": {"size": 1024},
+                                               "rot": {"dims": 64, "base": 1000000.0}}},
+        {"type": "gla", "mixer": {"heads": H, "dim": hd, "vdim": hd, "tau": 16.0, "a_rank": hd}},
+    ]
+    mlp = {"kind": "moe", "expert": {"ff": F // 8}, "shared": {"ff": F // 2},
+           "router": {"experts": 32, "top": 4, "groups": {"count": 4, "keep": 2}}}
+    j = {"architecture": "Dufizen", "vocab": V, "width": D, "norm": {"eps": 1e-5}, "token_side": {"dim": 256},
+         "layers": [dict(kinds[i % 2], mlp=mlp) for i in range(layers)]}
+    if layers >= 4:
+        j["loop"] = {"start": layers // 2 - 1, "stop": layers // 2 + 1, "times": 1}
+    return DufizenConfig.from_json(j)
+
+
 def run_design(args) -> int:
     import numpy as np
     import torch
@@ -300,9 +323,12 @@ def run_design(args) -> int:
     from ccinfer_b200.config import Qwen3Config
     from ccinfer_b200.engine.engine import Engine, EngineOptions, StepEntry
 
-    if args.design != "tugelorn":
+    # design -> (its configuration at a size, the closest model it is measured beside)
+    designs = {"tugelorn": (tugelorn_config, "qwen3"), "dufizen": (dufizen_config, "tugelorn")}
+    if args.design not in designs:
         print(json.dumps({"error": f"unknown design {args.design!r}"}))
         return 2
+    design_config, beside = designs[args.design]
     peaks = load_peaks()
     layers = args.layers or 6
     chunk, ctx, page = 2048, 2048, 16
@@ -351,7 +377,7 @@ def run_design(args) -> int:
         return B * steps / (ms * 1e-3), ms / steps, launches
 
     if args.design_profile:
-        cfg = tugelorn_config(args.design_sizes.split(",")[0], layers)
+        cfg = design_config(args.design_sizes.split(",")[0], layers)
         eng = engine(cfg, False)
         eng.open_request("p")
         eng.step([StepEntry("p", rng.randint(0, cfg.vocab, size=chunk).tolist(), [chunk - 1])])
@@ -366,11 +392,12 @@ def run_design(args) -> int:
         D, H, G, hd, F, V = DESIGN_SIZES[size]
         qwen = Qwen3Config.from_json(dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=D, num_attention_heads=H,
                                           num_key_value_heads=G, head_dim=hd, intermediate_size=F, vocab_size=V))
-        out = {"design": "tugelorn", "beside": "qwen3", "size": size, "layers": layers, "width": D, "q_heads": H,
+        other = qwen if beside == "qwen3" else designs[beside][0](size, layers)
+        out = {"design": args.design, "beside": beside, "size": size, "layers": layers, "width": D, "q_heads": H,
                "kv_heads": G, "head_dim": hd, "intermediate": F, "vocab": V, "dtype": "bf16",
                "data": "synthetic (random weights, random token ids)", "peaks": peaks.get("source", "measured"),
                "l2": "every step reads all weights, more than the 126 MB L2"}
-        for name, cfg in (("tugelorn", tugelorn_config(size, layers)), ("qwen3", qwen)):
+        for name, cfg in ((args.design, design_config(size, layers)), (beside, other)):
             sampler = ClockSampler()
             sampler.start()
             eng = engine(cfg, True)
@@ -386,7 +413,7 @@ def run_design(args) -> int:
             out[name] = r
             del eng
             torch.cuda.empty_cache()
-        out["ratio"] = {k: round(out["tugelorn"][k] / out["qwen3"][k], 3) for k in out["qwen3"] if k.endswith("tok_s")}
+        out["ratio"] = {k: round(out[args.design][k] / out[beside][k], 3) for k in out[beside] if k.endswith("tok_s")}
         print(json.dumps(out), flush=True)
     return 0
 
@@ -415,7 +442,8 @@ def main() -> int:
     ap.add_argument("--shape", default="8b", choices=["8b", "14b", "32b"], help="layer shape of --profile-steps")
     ap.add_argument("--workload", default="decode", choices=["decode", "mix14b", "long32b"],
                     help="decode (the default line) or one of the two other workloads of the benchmark record")
-    ap.add_argument("--design", default=None, help="tugelorn: that design beside Qwen3 at equal layer sizes")
+    ap.add_argument("--design", default=None, help="tugelorn (beside Qwen3) or dufizen (beside Tugelorn): that design beside its closest model at "
+                                                   "equal layer sizes")
     ap.add_argument("--design-sizes", default="mid,8b", help="layer sizes of --design: " + ", ".join(DESIGN_SIZES))
     ap.add_argument("--design-profile", action="store_true", help="with --design: a prompt and four eager decode steps")
     args = ap.parse_args()

@@ -19,6 +19,7 @@
 //
 // Scores, weights, sums and the rotation are float whatever the storage type.
 #include "common.cuh"
+#include "mma_common.cuh"
 #include <math_constants.h>
 
 using namespace ccb;
@@ -190,6 +191,267 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ cach
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// The same attention on tensor cores (bfloat16; R and r multiples of 16, R <= 512).
+//
+// All heads read the same cached rows, so the heads are the rows of the products: a block owns 16 rows, the
+// (query, head) pairs of hpb heads x 16 / hpb neighbouring queries, and walks the keys 32 at a time:
+//   S [16 x 32] = Q [16 x (R + r)] C^T        mma.sync m16n8k16; warp w takes the tile's keys 8 w .. 8 w + 7 over
+//                                              the whole width, Q and the keys from shared memory by ldmatrix
+//   softmax over the 32 keys                   float; maxima and sums meet in shared memory; P in bfloat16
+//   O [16 x R] += P [16 x 32] C [32 x R]       warp w takes the columns 16 (w + 4 i) .. + 15, keys by ldmatrix.trans
+// The cached rows arrive by cp.async, the next 32 while the current ones are used.  With few rows the key range
+// of a row is cut into `num_splits` pieces, one block each; a second kernel merges the pieces (the sink counts
+// in piece 0).  Rows of shared memory are 16 bytes longer than their data, so that the eight rows an ldmatrix
+// reads fall into different banks.
+constexpr int kMmaWarps = 4;
+constexpr int kMmaKeys = 32;
+
+template <int NPW>
+__global__ void __launch_bounds__(kMmaWarps * 32)
+latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* __restrict__ cache,
+                            const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
+                            __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                            int num_splits, const int* __restrict__ cu_q, const int* __restrict__ pos0,
+                            const int* __restrict__ entry_of_token, const int* __restrict__ block_table,
+                            int bt_stride, int entry0, int H, int R, int r, int page_size, int num_pages, int window,
+                            float scale, int hpb, int* status) {
+  ccb::pdl_begin();
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int W = R + r, LDW = W + 8;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [16][LDW]
+  __nv_bfloat16* Ct = Qs + 16 * LDW;                                            // [2][32][LDW]
+  __nv_bfloat16* Ps = Ct + 2 * kMmaKeys * LDW;                                  // [16][40]
+  float* red_max = reinterpret_cast<float*>(Ps + 16 * 40 + 32);                 // [4][16] (after 64 bytes of slack)
+  float* red_sum = red_max + kMmaWarps * 16;                                    // [4][16]
+  const int tq = 16 / hpb;
+  const int e = entry0 + blockIdx.z / num_splits, split = blockIdx.z % num_splits;
+  const int r0 = cu_q[e], n = cu_q[e + 1] - r0;
+  const int qbase = blockIdx.x * tq;
+  if (qbase >= n || entry_of_token[r0 + qbase] < 0) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  const int nq = min(tq, n - qbase);
+  const int p_first = pos0[e] + qbase, p_last = p_first + nq - 1;
+  const int j_lo = max(0, p_first - window + 1);
+  const int* bt = block_table + (size_t)e * bt_stride;
+  const int h0 = blockIdx.y * hpb;
+
+  // this thread's two rows of the 16: (query, head), whether they exist, their position
+  int row_t[2], row_h[2], row_p[2];
+  bool row_ok[2];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int rr = gid + 8 * hh, qi = rr / hpb, hd = h0 + rr % hpb;
+    row_ok[hh] = rr < tq * hpb && qi < nq && hd < H;
+    row_t[hh] = r0 + qbase + qi;
+    row_h[hh] = hd;
+    row_p[hh] = p_first + qi;
+  }
+  for (int i = threadIdx.x; i < 16 * W; i += kMmaWarps * 32) {
+    const int rr = i / W, c = i - rr * W, qi = rr / hpb, hd = h0 + rr % hpb;
+    const bool ok = rr < tq * hpb && qi < nq && hd < H;
+    Qs[rr * LDW + c] = __float2bfloat16_rn(ok ? qa[((size_t)(r0 + qbase + qi) * H + hd) * W + c] : 0.f);
+  }
+
+  const int tile0 = j_lo / kMmaKeys, n_tiles = p_last / kMmaKeys - tile0 + 1;
+  const int per = (n_tiles + num_splits - 1) / num_splits;
+  const int t_begin = tile0 + split * per, t_end = min(tile0 + n_tiles, t_begin + per);
+  const int chunks = W >> 3;   // 16-byte pieces of a row
+  auto fetch = [&](int tile, int buf) {
+    __nv_bfloat16* dst = Ct + (size_t)buf * kMmaKeys * LDW;
+    for (int i = threadIdx.x; i < kMmaKeys * chunks; i += kMmaWarps * 32) {
+      const int rr = i / chunks, c = i - rr * chunks;
+      const int j = tile * kMmaKeys + rr;
+      const __nv_bfloat16* src = cache;
+      bool ok = j >= j_lo && j <= p_last;
+      if (ok) {
+        const int lp = j / page_size;
+        const int page = lp < bt_stride ? bt[lp] : -1;
+        if (page < 0 || page >= num_pages) {
+          set_status(status, CCB_ST_BAD_PAGE);
+          ok = false;
+        } else {
+          src = cache + ((size_t)page * page_size + (j - lp * page_size)) * W + c * 8;
+        }
+      }
+      cp_async16(smem_u32(dst + rr * LDW + c * 8), src, ok);
+    }
+    cp_async_commit();
+  };
+
+  float m[2], l[2], acc[NPW][2][4];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const bool first = split == 0 && row_ok[hh];   // the sink: one term exp(sink) with no key and no value
+    m[hh] = first ? sink[row_h[hh]] : -CUDART_INF_F;
+    l[hh] = first ? 1.f : 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < NPW; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
+
+  const int n_pairs = R >> 4;
+  if (t_begin < t_end) fetch(t_begin, 0);
+  for (int tile = t_begin; tile < t_end; ++tile) {
+    const int buf = (tile - t_begin) & 1;
+    if (tile + 1 < t_end) {
+      fetch(tile + 1, buf ^ 1);
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();   // the tile (and, the first time, Q) is in shared memory for everyone
+    const __nv_bfloat16* C = Ct + (size_t)buf * kMmaKeys * LDW;
+    // ---- S = Q C^T for this warp's 8 keys
+    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint32_t q_addr = smem_u32(Qs + (lane & 15) * LDW + (lane >> 4) * 8);
+    const uint32_t k_addr = smem_u32(C + (8 * warp + (lane & 7)) * LDW + (lane >> 3) * 8);
+    const int ksteps = W >> 4;
+    for (int ks = 0; ks < ksteps; ks += 2) {
+      uint32_t b[4], a[4];
+      ldmatrix_x4(b[0], b[1], b[2], b[3], k_addr + ks * 32);
+      ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + ks * 32);
+      mma_bf16_16816(sc, a, b[0], b[1]);
+      if (ks + 1 < ksteps) {
+        ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + (ks + 1) * 32);
+        mma_bf16_16816(sc, a, b[2], b[3]);
+      }
+    }
+    // ---- softmax over the tile's 32 keys
+    const int jk = tile * kMmaKeys + 8 * warp + 2 * tig;
+    float mx[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int lo = max(0, row_p[hh] - window + 1);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const int j = jk + c;
+        const bool seen = row_ok[hh] && j >= lo && j <= row_p[hh];
+        sc[2 * hh + c] = seen ? sc[2 * hh + c] * scale : -CUDART_INF_F;
+      }
+      float v = fmaxf(sc[2 * hh], sc[2 * hh + 1]);
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+      mx[hh] = v;
+      if (tig == 0) red_max[warp * 16 + gid + 8 * hh] = v;
+    }
+    __syncthreads();
+    float corr[2];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float mn = m[hh];
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) mn = fmaxf(mn, red_max[w * 16 + gid + 8 * hh]);
+      const bool none = mn == -CUDART_INF_F;   // nothing seen so far (a piece without the sink)
+      corr[hh] = none ? 1.f : expf(m[hh] - mn);
+      m[hh] = mn;
+      const float p0 = none ? 0.f : expf(sc[2 * hh] - mn), p1 = none ? 0.f : expf(sc[2 * hh + 1] - mn);
+      float ps = p0 + p1;
+      ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+      ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+      if (tig == 0) red_sum[warp * 16 + gid + 8 * hh] = ps;
+      *reinterpret_cast<uint32_t*>(Ps + (gid + 8 * hh) * 40 + 8 * warp + 2 * tig) = pack_bf16(p0, p1);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      float ps = 0.f;
+#pragma unroll
+      for (int w = 0; w < kMmaWarps; ++w) ps += red_sum[w * 16 + gid + 8 * hh];
+      l[hh] = l[hh] * corr[hh] + ps;
+    }
+    // ---- O += P C for this warp's columns
+    uint32_t pa[2][4];
+    const uint32_t p_addr = smem_u32(Ps + (lane & 15) * 40 + (lane >> 4) * 8);
+    ldmatrix_x4(pa[0][0], pa[0][1], pa[0][2], pa[0][3], p_addr);
+    ldmatrix_x4(pa[1][0], pa[1][1], pa[1][2], pa[1][3], p_addr + 32);
+    const uint32_t v_addr = smem_u32(C + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDW + (lane >> 4) * 8);
+#pragma unroll
+    for (int i = 0; i < NPW; ++i) {
+      const int np = warp + kMmaWarps * i;
+      if (np < n_pairs) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          acc[i][j][0] *= corr[0]; acc[i][j][1] *= corr[0];
+          acc[i][j][2] *= corr[1]; acc[i][j][3] *= corr[1];
+        }
+#pragma unroll
+        for (int ks = 0; ks < 2; ++ks) {
+          uint32_t b[4];
+          ldmatrix_x4_trans(b[0], b[1], b[2], b[3], v_addr + (ks * 16 * LDW + np * 16) * 2);
+          mma_bf16_16816(acc[i][0], pa[ks], b[0], b[1]);
+          mma_bf16_16816(acc[i][1], pa[ks], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();   // everyone is done with this buffer, P and the exchange arrays
+  }
+  // ---- the rows leave: finished (one piece) or as a piece of a row
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    if (!row_ok[hh]) continue;
+    const size_t row = (size_t)row_t[hh] * H + row_h[hh];
+    if (num_splits == 1) {
+      const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)row_t[hh] * ldg + row_h[hh]])));
+      const float f = g / l[hh];
+#pragma unroll
+      for (int i = 0; i < NPW; ++i) {
+        const int np = warp + kMmaWarps * i;
+        if (np < n_pairs)
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            *reinterpret_cast<uint32_t*>(out + row * R + np * 16 + j * 8 + 2 * tig) =
+                pack_bf16(acc[i][j][2 * hh] * f, acc[i][j][2 * hh + 1] * f);
+      }
+    } else {
+      float* pa_out = part_acc + (row * num_splits + split) * R;
+#pragma unroll
+      for (int i = 0; i < NPW; ++i) {
+        const int np = warp + kMmaWarps * i;
+        if (np < n_pairs)
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            *reinterpret_cast<float2*>(pa_out + np * 16 + j * 8 + 2 * tig) =
+                make_float2(acc[i][j][2 * hh], acc[i][j][2 * hh + 1]);
+      }
+      if (warp == 0 && tig == 0) {
+        part_ml[(row * num_splits + split) * 2] = m[hh];
+        part_ml[(row * num_splits + split) * 2 + 1] = l[hh];
+      }
+    }
+  }
+}
+
+// out[t, h, :] = sigmoid(gate) * sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M); a warp per (token, head)
+__global__ void __launch_bounds__(256)
+latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int num_splits,
+                    const __nv_bfloat16* __restrict__ gate, int ldg, __nv_bfloat16* __restrict__ out,
+                    const int* __restrict__ entry_of_token, int row_begin, int n_rows, int H, int R) {
+  ccb::pdl_begin();
+  const int u = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (u >= n_rows * H) return;
+  const int t = row_begin + u / H, h = u % H;
+  if (entry_of_token[t] < 0) return;
+  const size_t row = (size_t)t * H + h;
+  float M = -CUDART_INF_F;
+  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
+  float L = 0.f;
+  for (int s = 0; s < num_splits; ++s)
+    L += part_ml[(row * num_splits + s) * 2 + 1] * expf(part_ml[(row * num_splits + s) * 2] - M);
+  const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + h])));
+  for (int c = lane; c < R; c += 32) {
+    float v = 0.f;
+    for (int s = 0; s < num_splits; ++s) {
+      const float ms = part_ml[(row * num_splits + s) * 2];
+      if (ms != -CUDART_INF_F) v += part_acc[(row * num_splits + s) * R + c] * expf(ms - M);
+    }
+    out[row * R + c] = __float2bfloat16_rn(v * g / L);
+  }
+}
+
 template <typename T, int NV>
 int launch_attention(const float* qa, const void* cache, const float* sink, const void* gate, int ldg, void* out,
                      const int* cu_q, const int* pos0, const int* eot, const int* block_table, int bt_stride, int entry0, int n_entries,
@@ -266,4 +528,61 @@ CCB_API int ccb_latent_attention(const float* qa, const void* cache, const float
                                          n_entries, max_q, H, R, r, page_size, num_pages, window, scale, status,
                                          stream);
   return CCB_REFUSE_DTYPE;
+}
+
+namespace {
+template <int NPW>
+int launch_mma(const float* qa, const void* cache, const float* sink, const void* gate, int ldg, void* out,
+               float* part_acc, float* part_ml, int num_splits, const int* cu_q, const int* pos0, const int* eot,
+               const int* block_table, int bt_stride, int entry0, int n_entries, int max_q, int H, int R, int r,
+               int page_size, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+  int hpb = 1;
+  while (hpb < 16 && hpb < H) hpb *= 2;
+  const int tq = 16 / hpb;
+  const int W = R + r;
+  const size_t smem = (size_t)(16 + 2 * kMmaKeys) * (W + 8) * 2 + 16 * 40 * 2 + 64 + 2 * kMmaWarps * 16 * 4 + 64;
+  cudaFuncSetAttribute(latent_attention_mma_kernel<NPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  dim3 grid((max_q + tq - 1) / tq, (H + hpb - 1) / hpb, n_entries * num_splits);
+  ccb_launch(latent_attention_mma_kernel<NPW>, grid, dim3(kMmaWarps * 32), smem, stream, qa,
+             (const __nv_bfloat16*)cache, sink, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, part_acc,
+             part_ml, num_splits, cu_q, pos0, eot, block_table, bt_stride, entry0, H, R, r, page_size, num_pages,
+             window, scale, hpb, status);
+  return ccb_launch_status();
+}
+}  // namespace
+
+// Whether the tensor-core form takes these sizes (bfloat16 only).
+CCB_API int ccb_latent_attention_mma_fits(int R, int r) {
+  return (R > 0 && R % 16 == 0 && r >= 0 && r % 16 == 0 && R <= 512) ? 1 : 0;
+}
+
+// As ccb_latent_attention, bfloat16, for single-token entries with `num_splits` > 1: entries entry0 .. are the
+// token rows entry0 .. (a step lists its single tokens first), part_acc [rows * H * num_splits * R] and part_ml
+// [rows * H * num_splits * 2] are float scratch.
+CCB_API int ccb_latent_attention_mma(const float* qa, const void* cache, const float* sink, const void* gate, int ldg,
+                                     void* out, float* part_acc, float* part_ml, int num_splits, const int* cu_q,
+                                     const int* pos0, const int* entry_of_token, const int* block_table,
+                                     int bt_stride, int entry0, int n_entries, int max_q, int H, int R, int r,
+                                     int page_size, int num_pages, int window, float scale, int* status,
+                                     cudaStream_t stream) {
+  if (n_entries <= 0 || max_q <= 0) return 0;
+  if (!ccb_latent_attention_mma_fits(R, r) || H <= 0 || page_size <= 0 || window <= 0 || num_splits < 1 ||
+      (long long)n_entries * num_splits > 65535 || (num_splits > 1 && (max_q != 1 || !part_acc || !part_ml)))
+    return CCB_REFUSE_SIZE;
+  const int pairs_per_warp = ((R >> 4) + kMmaWarps - 1) / kMmaWarps;
+  int rc;
+#define CCB_LMMA(NPW)                                                                                              \
+  rc = launch_mma<NPW>(qa, cache, sink, gate, ldg, out, part_acc, part_ml, num_splits, cu_q, pos0, entry_of_token, \
+                       block_table, bt_stride, entry0, n_entries, max_q, H, R, r, page_size, num_pages, window, scale, \
+                       status, stream)
+  if (pairs_per_warp <= 1) CCB_LMMA(1);
+  else if (pairs_per_warp <= 2) CCB_LMMA(2);
+  else if (pairs_per_warp <= 4) CCB_LMMA(4);
+  else CCB_LMMA(8);
+#undef CCB_LMMA
+  if (rc != 0 || num_splits == 1) return rc;
+  const int units = n_entries * H;
+  ccb_launch(latent_merge_kernel, dim3((units + 7) / 8), dim3(256), 0, stream, part_acc, part_ml, num_splits,
+             (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, entry_of_token, entry0, n_entries, H, R);
+  return ccb_launch_status();
 }

@@ -85,6 +85,10 @@ _SIGNATURES = {
     "ccb_latent_attention": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                              c_int, c_void_p, c_void_p],
+    "ccb_latent_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                 c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "ccb_latent_attention_mma_fits": [c_int, c_int],
     "ccb_moe_route": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                       c_void_p],
     "ccb_moe_dense_act": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -524,6 +528,48 @@ def latent_attention(qa, cache, sink, gate, out, cu_q, pos0, entry_of_token, blo
                                       float(scale), _dt(out), _p(status), _stream()), "latent_attention")
 
 
+def latent_attention_mma_fits(dtype, R: int, r: int) -> bool:
+    """Whether the tensor-core form of latent attention takes these sizes."""
+    return dtype == torch.bfloat16 and R % 16 == 0 and r % 16 == 0 and 0 < R <= 512
+
+
+LATENT_MMA_KEYS = 32       # keys a block of the tensor-core form takes at a time
+LATENT_MMA_ROWS = 16       # (query, head) rows of a block
+
+
+def latent_attention_splits(n_rows: int, H: int, window: int) -> int:
+    """Into how many pieces the key range of single-token rows is cut: enough blocks for two per SM, at most one
+    piece per 32 keys.  It depends on the number of rows only, so a step of a given size launches one grid."""
+    groups = -(-H // min(LATENT_MMA_ROWS, H))
+    most = -(-window // LATENT_MMA_KEYS) + 1
+    return max(1, min(most, split_target_blocks() // max(1, n_rows * groups)))
+
+
+def latent_attention_mma(qa, cache, sink, gate, out, cu_q, pos0, entry_of_token, block_table, entry0: int,
+                         n_entries: int, max_q: int, page_size: int, window: int, scale: float, num_splits: int = 1,
+                         part_acc=None, part_ml=None, status=None) -> None:
+    """``latent_attention`` on tensor cores (bfloat16; see latent_attention_mma_fits).  ``num_splits`` > 1 (single
+    tokens only): the key range of a row is cut into pieces that a second kernel merges; part_acc float
+    [rows * H * num_splits * R], part_ml float [rows * H * num_splits * 2]."""
+    _cuda(qa, cache, sink, out, cu_q, pos0, entry_of_token, block_table, part_acc, part_ml, status)
+    T, H, W = qa.shape
+    R = out.shape[2]
+    assert out.shape == (T, H, R) and cache.shape[1:] == (page_size, W)
+    assert out.dtype == cache.dtype == gate.dtype == torch.bfloat16
+    assert sink.dtype == torch.float32 and sink.numel() == H and gate.stride(1) == 1 and qa.dtype == torch.float32
+    if num_splits > 1:
+        assert part_acc.dtype == part_ml.dtype == torch.float32 and max_q == 1
+        assert part_acc.numel() >= (entry0 + n_entries) * H * num_splits * R
+        assert part_ml.numel() >= (entry0 + n_entries) * H * num_splits * 2
+    _check(lib().ccb_latent_attention_mma(_p(qa), _p(cache), _p(sink), _p(gate), gate.stride(0), _p(out), _p(part_acc),
+                                          _p(part_ml), num_splits, _p(cu_q), _p(pos0), _p(entry_of_token),
+                                          _p(block_table), block_table.stride(0), entry0, n_entries, max_q, H, R,
+                                          W - R, page_size, cache.shape[0], int(window), float(scale), _p(status),
+                                          _stream()), "latent_attention_mma")
+    if num_splits > 1:
+        counters.own += 1   # the merge kernel
+
+
 def moe_route(logits, correction, idx, wts, dense_w, groups: int, keep: int) -> None:
     """The router's choice per token from float logits [T, E]: softmax scores, + ``correction`` for the choice,
     only experts of the ``keep`` best of ``groups`` groups of neighbours, the top idx.shape[1] of them.
@@ -580,14 +626,6 @@ def moe_grouped(c, a, src_row, w, w_expert_stride: int, row_w, tile_e, tile_r0, 
     _check(lib().ccb_moe_grouped(_p(a), a.stride(0), _p(src_row), _p(w), w.stride(0), int(w_expert_stride), _p(c),
                                  c.stride(0), _p(row_w), _p(tile_e), _p(tile_r0), _p(tile_n), tile_e.numel(), N, K, BM,
                                  mode, _dt(a), _stream()), "moe_grouped")
-
-
-def moe_grouped_fits(dtype, K1: int, K2: int, *tensors) -> bool:
-    """Whether the grouped products take these operands: float always; bfloat16 with 16-byte rows."""
-    if dtype == torch.float32:
-        return True
-    return (K1 % 8 == 0 and K2 % 8 == 0
-            and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in tensors))
 
 
 def moe_combine(out, rows, pair_pos, shared, top: int) -> None:

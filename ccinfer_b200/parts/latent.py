@@ -104,11 +104,29 @@ class LatentAttention(Mixer):
         ol = rt.scratch.get("latent_o", (rt.max_tokens, H, R), rt.dtype)[:T]
         gate = proj[:, self.og:self.og + H]
         args = (qa, rows, self.sink, gate, ol, step.cu_q, step.pos0, step.entry_of_token, g.block_table)
-        if step.n_single > 0:    # the step's single tokens come first: a block per token and eight heads
-            kernels.latent_attention(*args, 0, step.n_single, 1, g.page_size, self.window, self.scale, status=rt.status)
-        if step.n_entries > step.n_single:
-            kernels.latent_attention(*args, step.n_single, step.n_entries - step.n_single, step.max_q_len,
-                                     g.page_size, self.window, self.scale, status=rt.status)
+        n1, many = step.n_single, step.n_entries - step.n_single
+        if kernels.latent_attention_mma_fits(rt.dtype, R, r):
+            # tensor cores: the heads are the rows of the products.  The step's single tokens come first; their
+            # key ranges are cut into pieces so that a few rows still fill the machine
+            if n1 > 0:
+                splits = kernels.latent_attention_splits(n1, H, self.window)
+                acc = ml = None
+                if splits > 1:
+                    most = kernels.latent_attention_splits(1, H, self.window)   # (rows x pieces is bounded by the target)
+                    cap = max(rt.max_entries * H * most, kernels.split_target_blocks() * kernels.LATENT_MMA_ROWS * 2)
+                    acc = rt.scratch.get("latent_part_acc", (cap * R,), torch.float32)
+                    ml = rt.scratch.get("latent_part_ml", (cap * 2,), torch.float32)
+                kernels.latent_attention_mma(*args, 0, n1, 1, g.page_size, self.window, self.scale, splits, acc, ml,
+                                             status=rt.status)
+            if many > 0:
+                kernels.latent_attention_mma(*args, n1, many, step.max_q_len, g.page_size, self.window, self.scale,
+                                             status=rt.status)
+        else:   # the plain kernel: float, and sizes that are multiples of nothing
+            if n1 > 0:
+                kernels.latent_attention(*args, 0, n1, 1, g.page_size, self.window, self.scale, status=rt.status)
+            if many > 0:
+                kernels.latent_attention(*args, n1, many, step.max_q_len, g.page_size, self.window, self.scale,
+                                         status=rt.status)
         o = rt.scratch.get("latent_v", (rt.max_tokens, H, dv), rt.dtype)[:T]
         rt.linear_batched(o.permute(1, 0, 2), ol.permute(1, 0, 2), self.w_uv)
         out = rt.scratch.get("attn_out", (rt.max_tokens, self.hidden), rt.dtype)[:T]

@@ -18,7 +18,7 @@ Two forms, chosen by size (``sparse=`` forces one):
   kernel adds each token's rows up in the order of its choices.  A decode step then reads the chosen experts'
   weights and no others.
 
-Both forms use the same merged weight tensors.
+Which form runs is settled when the weights are bound, and the weights are merged for that form.
 """
 from __future__ import annotations
 
@@ -67,11 +67,18 @@ class MixtureOfExperts(FeedForward):
         self.correction = fetch(n["correction"]).float().contiguous() if n.get("correction") else None
         ups = [fetch(n["up"].format(e=e)) for e in range(self.E)]
         downs = [fetch(n["down"].format(e=e)) for e in range(self.E)]
-        if self.SF:
+        # which form runs is settled here, by the sizes: the grouped products want 16-byte rows in bfloat16
+        fits = rt.dtype == torch.float32 or (self.hidden % 8 == 0 and self.F % 8 == 0)
+        big = 2 * self.E * self.F * self.hidden >= self.SPARSE_MIN_WEIGHTS
+        self.use_sparse = fits and (big if self.sparse is None else bool(self.sparse))
+        self.w_shared_up = self.w_shared_down = None
+        if self.SF and self.use_sparse:      # the shared expert is two products of its own
+            self.w_shared_up, self.w_shared_down = fetch(n["shared_up"]), fetch(n["shared_down"])
+        elif self.SF:                        # its rows and columns come after the experts'
             ups.append(fetch(n["shared_up"]))
             downs.append(fetch(n["shared_down"]))
-        self.w_up = torch.cat(ups, dim=0).contiguous()        # [E F + SF, D]
-        self.w_down = torch.cat(downs, dim=1).contiguous()    # [D, E F + SF]
+        self.w_up = torch.cat(ups, dim=0).contiguous()        # [E F (+ SF), D]
+        self.w_down = torch.cat(downs, dim=1).contiguous()    # [D, E F (+ SF)]
 
     def route(self, x, T):
         """idx int32 [T, top], wts float [T, top], dense float [T, E] for the rows of x."""
@@ -83,12 +90,6 @@ class MixtureOfExperts(FeedForward):
         dense = rt.scratch.get("moe_dense", (rt.max_tokens, self.E), torch.float32)[:T]
         kernels.moe_route(logits, self.correction, idx, wts, dense, self.groups, self.keep)
         return idx, wts, dense
-
-    def _use_sparse(self, x) -> bool:
-        fits = kernels.moe_grouped_fits(self.rt.dtype, self.hidden, self.F, x, self.w_up, self.w_down)
-        if self.sparse is not None:
-            return bool(self.sparse) and fits
-        return fits and 2 * self.E * self.F * self.hidden >= self.SPARSE_MIN_WEIGHTS
 
     def _forward_sparse(self, x, T):
         rt = self.rt
@@ -112,10 +113,10 @@ class MixtureOfExperts(FeedForward):
         shared = None
         if self.SF:
             sa = rt.scratch.get("moe_shared_act", (rt.max_tokens, self.SF), rt.dtype)[:T]
-            rt.linear(sa, x, self.w_up[E * F:])
+            rt.linear(sa, x, self.w_shared_up)
             kernels.moe_dense_act(sa, wts, 0, 1, self.SF)
             shared = rt.scratch.get("moe_shared_out", (rt.max_tokens, D), rt.dtype)[:T]
-            rt.linear(shared, sa, self.w_down[:, E * F:])
+            rt.linear(shared, sa, self.w_shared_down)
         out = rt.scratch.get("ffn_out", (rt.max_tokens, D), rt.dtype)[:T]
         kernels.moe_combine(out, rows, pair_pos, shared, top)
         return out
@@ -124,7 +125,7 @@ class MixtureOfExperts(FeedForward):
         rt = self.rt
         x = rt.rows(x)
         T = x.shape[0]
-        if self._use_sparse(x):
+        if self.use_sparse:
             return self._forward_sparse(x, T)
         _, _, dense = self.route(x, T)
         act = rt.scratch.get("moe_act", (rt.max_tokens, self.width), rt.dtype)[:T]

@@ -222,7 +222,7 @@ def test_mixture_of_experts_alone(dtype, sparse, E, top, F, D, groups, SF):
              "shared_up": "shared.up", "shared_down": "shared.down"}
     part = MixtureOfExperts(D, E, top, F, names, *(groups or (1, 1)), SF, sparse=sparse)
     part.bind(rt, lambda n: W[n].cuda().to(dtype) if W[n].dim() == 2 else W[n].cuda())
-    assert part._use_sparse(torch.empty(1, D, dtype=dtype, device="cuda")) == sparse
+    assert part.use_sparse == sparse
     for T in (1, 5, 70, 300, 640):
         x = torch.randn(T, D, generator=g).to(torch.bfloat16)
         want = plain.moe(x.double(), {k: v.double() for k, v in W.items()}, "", m)
@@ -302,7 +302,11 @@ def test_gated_linear_recurrence_kernels(dk, dv, H):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,d,r,dims,dv,R,window,page", [(3, 16, 8, 8, 12, 32, 24, 8), (1, 10, 6, 4, 14, 20, 9, 4),
                                                          (8, 32, 16, 16, 32, 64, 70, 16), (2, 8, 4, 4, 8, 40, 1, 4),
-                                                         (11, 4, 2, 2, 4, 12, 300, 16)])
+                                                         (11, 4, 2, 2, 4, 12, 300, 16),
+                                                         # sizes that the tensor-core form takes in bfloat16
+                                                         (3, 16, 16, 16, 12, 32, 24, 8), (20, 8, 16, 8, 8, 48, 300, 8),
+                                                         (1, 16, 32, 32, 16, 512, 40, 16),
+                                                         (16, 16, 16, 16, 16, 128, 100, 16)])
 def test_latent_attention_mixer_alone(dtype, H, d, r, dims, dv, R, window, page, tmp_path):
     """One layer of latent attention as a whole model would hide it behind other layers, so the mixer runs in a
     step of its own: a prompt, then portions and single tokens from the cache, against the plain mixer."""
