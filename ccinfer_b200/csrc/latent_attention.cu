@@ -257,10 +257,10 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
   const int per = (n_tiles + num_splits - 1) / num_splits;
   const int t_begin = tile0 + split * per, t_end = min(tile0 + n_tiles, t_begin + per);
   const int chunks = W >> 3;   // 16-byte pieces of a row
-  auto fetch = [&](int tile, int buf) {
+  auto fetch = [&](int tile, int buf) {   // a warp takes every fourth row; its page is looked up once
     __nv_bfloat16* dst = Ct + (size_t)buf * kMmaKeys * LDW;
-    for (int i = threadIdx.x; i < kMmaKeys * chunks; i += kMmaWarps * 32) {
-      const int rr = i / chunks, c = i - rr * chunks;
+#pragma unroll 2
+    for (int rr = warp; rr < kMmaKeys; rr += kMmaWarps) {
       const int j = tile * kMmaKeys + rr;
       const __nv_bfloat16* src = cache;
       bool ok = j >= j_lo && j <= p_last;
@@ -268,13 +268,14 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
         const int lp = j / page_size;
         const int page = lp < bt_stride ? bt[lp] : -1;
         if (page < 0 || page >= num_pages) {
-          set_status(status, CCB_ST_BAD_PAGE);
+          if (lane == 0) set_status(status, CCB_ST_BAD_PAGE);
           ok = false;
         } else {
-          src = cache + ((size_t)page * page_size + (j - lp * page_size)) * W + c * 8;
+          src = cache + ((size_t)page * page_size + (j - lp * page_size)) * W;
         }
       }
-      cp_async16(smem_u32(dst + rr * LDW + c * 8), src, ok);
+      const uint32_t d = smem_u32(dst + rr * LDW);
+      for (int c = lane; c < chunks; c += 32) cp_async16(d + c * 16, src + (ok ? c * 8 : 0), ok);
     }
     cp_async_commit();
   };
@@ -306,20 +307,21 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
     __syncthreads();   // the tile (and, the first time, Q) is in shared memory for everyone
     const __nv_bfloat16* C = Ct + (size_t)buf * kMmaKeys * LDW;
     // ---- S = Q C^T for this warp's 8 keys
-    float sc[4] = {0.f, 0.f, 0.f, 0.f};
+    float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc_odd[4] = {0.f, 0.f, 0.f, 0.f};   // two chains of products
     const uint32_t q_addr = smem_u32(Qs + (lane & 15) * LDW + (lane >> 4) * 8);
     const uint32_t k_addr = smem_u32(C + (8 * warp + (lane & 7)) * LDW + (lane >> 3) * 8);
     const int ksteps = W >> 4;
+#pragma unroll 3
     for (int ks = 0; ks < ksteps; ks += 2) {
-      uint32_t b[4], a[4];
+      uint32_t b[4], a[4], a2[4];
       ldmatrix_x4(b[0], b[1], b[2], b[3], k_addr + ks * 32);
       ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + ks * 32);
+      if (ks + 1 < ksteps) ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], q_addr + (ks + 1) * 32);
       mma_bf16_16816(sc, a, b[0], b[1]);
-      if (ks + 1 < ksteps) {
-        ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + (ks + 1) * 32);
-        mma_bf16_16816(sc, a, b[2], b[3]);
-      }
+      if (ks + 1 < ksteps) mma_bf16_16816(sc_odd, a2, b[2], b[3]);
     }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sc[i] += sc_odd[i];
     // ---- softmax over the tile's 32 keys
     const int jk = tile * kMmaKeys + 8 * warp + 2 * tig;
     float mx[2];
@@ -425,30 +427,45 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
   }
 }
 
-// out[t, h, :] = sigmoid(gate) * sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M); a warp per (token, head)
-__global__ void __launch_bounds__(256)
+// out[t, h, :] = sigmoid(gate) * sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M); a block per (token, head),
+// a thread per column; the pieces' factors are worked out once, by the first warp
+constexpr int kMergeThreads = 128;
+constexpr int kMergeMaxSplits = 64;
+
+__global__ void __launch_bounds__(kMergeThreads)
 latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int num_splits,
                     const __nv_bfloat16* __restrict__ gate, int ldg, __nv_bfloat16* __restrict__ out,
-                    const int* __restrict__ entry_of_token, int row_begin, int n_rows, int H, int R) {
+                    const int* __restrict__ entry_of_token, int row_begin, int H, int R) {
   ccb::pdl_begin();
-  const int u = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (u >= n_rows * H) return;
-  const int t = row_begin + u / H, h = u % H;
+  __shared__ float f[kMergeMaxSplits];
+  const int t = row_begin + blockIdx.x / H, h = blockIdx.x % H;
   if (entry_of_token[t] < 0) return;
   const size_t row = (size_t)t * H + h;
-  float M = -CUDART_INF_F;
-  for (int s = 0; s < num_splits; ++s) M = fmaxf(M, part_ml[(row * num_splits + s) * 2]);
-  float L = 0.f;
-  for (int s = 0; s < num_splits; ++s)
-    L += part_ml[(row * num_splits + s) * 2 + 1] * expf(part_ml[(row * num_splits + s) * 2] - M);
-  const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + h])));
-  for (int c = lane; c < R; c += 32) {
-    float v = 0.f;
-    for (int s = 0; s < num_splits; ++s) {
-      const float ms = part_ml[(row * num_splits + s) * 2];
-      if (ms != -CUDART_INF_F) v += part_acc[(row * num_splits + s) * R + c] * expf(ms - M);
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float ms[2], ls[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int s = lane + 32 * i;
+      ms[i] = s < num_splits ? part_ml[(row * num_splits + s) * 2] : -CUDART_INF_F;
+      ls[i] = s < num_splits ? part_ml[(row * num_splits + s) * 2 + 1] : 0.f;
     }
-    out[row * R + c] = __float2bfloat16_rn(v * g / L);
+    const float M = warp_max(fmaxf(ms[0], ms[1]));   // finite: piece 0 holds the sink
+    float e[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) e[i] = ms[i] == -CUDART_INF_F ? 0.f : expf(ms[i] - M);
+    const float L = warp_sum(ls[0] * e[0] + ls[1] * e[1]);
+    const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)t * ldg + h])));
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (lane + 32 * i < num_splits) f[lane + 32 * i] = e[i] * g / L;
+  }
+  __syncthreads();
+  const float* pa = part_acc + row * num_splits * R;
+  for (int c = threadIdx.x; c < R; c += kMergeThreads) {
+    float v = 0.f;
+    for (int s = 0; s < num_splits; ++s) v = fmaf(pa[(size_t)s * R + c], f[s], v);
+    out[row * R + c] = __float2bfloat16_rn(v);
   }
 }
 
@@ -567,7 +584,7 @@ CCB_API int ccb_latent_attention_mma(const float* qa, const void* cache, const f
                                      cudaStream_t stream) {
   if (n_entries <= 0 || max_q <= 0) return 0;
   if (!ccb_latent_attention_mma_fits(R, r) || H <= 0 || page_size <= 0 || window <= 0 || num_splits < 1 ||
-      (long long)n_entries * num_splits > 65535 || (num_splits > 1 && (max_q != 1 || !part_acc || !part_ml)))
+      (long long)n_entries * num_splits > 65535 || num_splits > kMergeMaxSplits || (num_splits > 1 && (max_q != 1 || !part_acc || !part_ml)))
     return CCB_REFUSE_SIZE;
   const int pairs_per_warp = ((R >> 4) + kMmaWarps - 1) / kMmaWarps;
   int rc;
@@ -581,8 +598,7 @@ CCB_API int ccb_latent_attention_mma(const float* qa, const void* cache, const f
   else CCB_LMMA(8);
 #undef CCB_LMMA
   if (rc != 0 || num_splits == 1) return rc;
-  const int units = n_entries * H;
-  ccb_launch(latent_merge_kernel, dim3((units + 7) / 8), dim3(256), 0, stream, part_acc, part_ml, num_splits,
-             (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, entry_of_token, entry0, n_entries, H, R);
+  ccb_launch(latent_merge_kernel, dim3(n_entries * H), dim3(kMergeThreads), 0, stream, part_acc, part_ml, num_splits,
+             (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, entry_of_token, entry0, H, R);
   return ccb_launch_status();
 }

@@ -236,7 +236,8 @@ __device__ __forceinline__ uint4 ld16_or_zero(const __nv_bfloat16* p, bool ok) {
 
 // MODE 0: C (compute type) = relu(c)^2 * row_w[row];  MODE 1: C (float) = c.
 // A [*, lda]: row src_row[r] (MODE 0) or r itself (src_row null).  W_e = W + e * w_expert_stride, rows at ldw.
-template <int MT, int NT, int MODE>
+// DEPTH: steps of 32 k whose operands are loaded together (few rows: more bytes in flight per thread).
+template <int MT, int NT, int DEPTH, int MODE>
 __global__ void __launch_bounds__(128)
 moe_grouped_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ src_row,
                         const __nv_bfloat16* __restrict__ W, int ldw, long long w_expert_stride,
@@ -280,36 +281,44 @@ moe_grouped_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
 
-  uint4 a[MT][2], b[NT];
+  uint4 a[DEPTH][MT][2], b[DEPTH][NT];
   auto load = [&](int k0) {
-    const int k = k0 + 8 * tig;
-    const bool ok = k < K;
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      a[m][0] = ld16_or_zero(arow[m][0] + k, ok);
-      a[m][1] = ld16_or_zero(arow[m][1] + k, ok);
+    for (int d = 0; d < DEPTH; ++d) {
+      const int k = k0 + 32 * d + 8 * tig;
+      const bool ok = k < K;
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        a[d][m][0] = ld16_or_zero(arow[m][0] + k, ok);
+        a[d][m][1] = ld16_or_zero(arow[m][1] + k, ok);
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) b[d][n] = ld16_or_zero(wrow[n] + k, ok && wok[n]);
     }
-#pragma unroll
-    for (int n = 0; n < NT; ++n) b[n] = ld16_or_zero(wrow[n] + k, ok && wok[n]);
   };
   load(0);
-  for (int k0 = 0; k0 < K; k0 += 32) {
-    uint4 ca[MT][2], cb[NT];
+  for (int k0 = 0; k0 < K; k0 += 32 * DEPTH) {
+    uint4 ca[DEPTH][MT][2], cb[DEPTH][NT];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) ca[m][0] = a[m][0], ca[m][1] = a[m][1];
+    for (int d = 0; d < DEPTH; ++d) {
 #pragma unroll
-    for (int n = 0; n < NT; ++n) cb[n] = b[n];
-    if (k0 + 32 < K) load(k0 + 32);   // the next step's operands are on their way during this step's products
+      for (int m = 0; m < MT; ++m) ca[d][m][0] = a[d][m][0], ca[d][m][1] = a[d][m][1];
 #pragma unroll
-    for (int m = 0; m < MT; ++m) {
-      const uint32_t f0[4] = {ca[m][0].x, ca[m][1].x, ca[m][0].y, ca[m][1].y};
-      const uint32_t f1[4] = {ca[m][0].z, ca[m][1].z, ca[m][0].w, ca[m][1].w};
-#pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        mma_bf16_16816(acc[m][n], f0, cb[n].x, cb[n].y);
-        mma_bf16_16816(acc[m][n], f1, cb[n].z, cb[n].w);
-      }
+      for (int n = 0; n < NT; ++n) cb[d][n] = b[d][n];
     }
+    if (k0 + 32 * DEPTH < K) load(k0 + 32 * DEPTH);   // the next operands are on their way during these products
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d)
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const uint32_t f0[4] = {ca[d][m][0].x, ca[d][m][1].x, ca[d][m][0].y, ca[d][m][1].y};
+        const uint32_t f1[4] = {ca[d][m][0].z, ca[d][m][1].z, ca[d][m][0].w, ca[d][m][1].w};
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+          mma_bf16_16816(acc[m][n], f0, cb[d][n].x, cb[d][n].y);
+          mma_bf16_16816(acc[m][n], f1, cb[d][n].z, cb[d][n].w);
+        }
+      }
   }
 #pragma unroll
   for (int m = 0; m < MT; ++m)
@@ -444,13 +453,15 @@ CCB_API int ccb_moe_grouped(const void* A, int lda, const int* src_row, const vo
   if (K % 8 || lda % 8 || ldw % 8 || w_expert_stride % 8 || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(W) & 15))
     return CCB_REFUSE_SIZE;
-  dim3 grid(max_tiles, (N + 127) / 128);
-#define CCB_GROUPED(MT, MODE)                                                                                     \
-  ccb_launch(moe_grouped_bf16_kernel<MT, 4, MODE>, grid, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row, \
-             (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K)
-  if (BM == 16) { if (mode == 0) CCB_GROUPED(1, 0); else CCB_GROUPED(1, 1); }
-  else if (BM == 32) { if (mode == 0) CCB_GROUPED(2, 0); else CCB_GROUPED(2, 1); }
-  else if (BM == 64) { if (mode == 0) CCB_GROUPED(4, 0); else CCB_GROUPED(4, 1); }
+  // few rows an expert (tiles of 16): a block takes 32 columns only and loads four steps of k at once, so that
+  // a decode step has enough blocks and bytes in flight to stream the chosen experts' weights
+#define CCB_GROUPED(MT, NT, DEPTH, MODE)                                                                          \
+  ccb_launch(moe_grouped_bf16_kernel<MT, NT, DEPTH, MODE>, dim3(max_tiles, (N + 32 * NT - 1) / (32 * NT)), dim3(128), \
+             0, stream, (const __nv_bfloat16*)A, lda, src_row, (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, \
+             row_w, tile_e, tile_r0, tile_n, N, K)
+  if (BM == 16) { if (mode == 0) CCB_GROUPED(1, 1, 4, 0); else CCB_GROUPED(1, 1, 4, 1); }
+  else if (BM == 32) { if (mode == 0) CCB_GROUPED(2, 4, 1, 0); else CCB_GROUPED(2, 4, 1, 1); }
+  else if (BM == 64) { if (mode == 0) CCB_GROUPED(4, 4, 1, 0); else CCB_GROUPED(4, 4, 1, 1); }
   else return CCB_REFUSE_SIZE;
 #undef CCB_GROUPED
   return ccb_launch_status();

@@ -541,7 +541,7 @@ def latent_attention_splits(n_rows: int, H: int, window: int) -> int:
     """Into how many pieces the key range of single-token rows is cut: enough blocks for two per SM, at most one
     piece per 32 keys.  It depends on the number of rows only, so a step of a given size launches one grid."""
     groups = -(-H // min(LATENT_MMA_ROWS, H))
-    most = -(-window // LATENT_MMA_KEYS) + 1
+    most = min(64, -(-window // LATENT_MMA_KEYS) + 1)
     return max(1, min(most, split_target_blocks() // max(1, n_rows * groups)))
 
 
