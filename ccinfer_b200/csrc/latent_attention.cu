@@ -204,11 +204,13 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ cach
 // of a row is cut into `num_splits` pieces, one block each; a second kernel merges the pieces (the sink counts
 // in piece 0).  Rows of shared memory are 16 bytes longer than their data, so that the eight rows an ldmatrix
 // reads fall into different banks.
-constexpr int kMmaWarps = 4;
-constexpr int kMmaKeys = 32;
+constexpr int kMmaWarps = 4;   // of a block of single tokens
 
-template <int NPW>
-__global__ void __launch_bounds__(kMmaWarps * 32)
+// MTL: tiles of 16 rows a block; WARPS: its warps, each with 8 of the 8 * WARPS keys staged at a time.  Single
+// tokens: 16 rows, 4 warps, 32 keys (two blocks an SM).  Portions of prompts: 32 rows, 8 warps, 64 keys (one
+// block an SM): twice the queries share every staged key and the block meets at its barriers half as often.
+template <int NPW, int MTL, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32)
 latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* __restrict__ cache,
                             const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
                             __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
@@ -217,14 +219,15 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
                             int bt_stride, int entry0, int H, int R, int r, int page_size, int num_pages, int window,
                             float scale, int hpb, int* status) {
   ccb::pdl_begin();
+  constexpr int ROWS = 16 * MTL, KEYS = 8 * WARPS, LDP = KEYS + 8;
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int W = R + r, LDW = W + 8;
-  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [16][LDW]
-  __nv_bfloat16* Ct = Qs + 16 * LDW;                                            // [2][32][LDW]
-  __nv_bfloat16* Ps = Ct + 2 * kMmaKeys * LDW;                                  // [16][40]
-  float* red_max = reinterpret_cast<float*>(Ps + 16 * 40 + 32);                 // [4][16] (after 64 bytes of slack)
-  float* red_sum = red_max + kMmaWarps * 16;                                    // [4][16]
-  const int tq = 16 / hpb;
+  __nv_bfloat16* Qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);              // [ROWS][LDW]
+  __nv_bfloat16* Ct = Qs + ROWS * LDW;                                          // [2][KEYS][LDW]
+  __nv_bfloat16* Ps = Ct + 2 * KEYS * LDW;                                  // [ROWS][LDP]
+  float* red_max = reinterpret_cast<float*>(Ps + ROWS * LDP + 32);               // [4][ROWS] (after 64 bytes of slack)
+  float* red_sum = red_max + WARPS * ROWS;                                  // [4][ROWS]
+  const int tq = ROWS / hpb;
   const int e = entry0 + blockIdx.z / num_splits, split = blockIdx.z % num_splits;
   const int r0 = cu_q[e], n = cu_q[e + 1] - r0;
   const int qbase = blockIdx.x * tq;
@@ -236,32 +239,34 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
   const int* bt = block_table + (size_t)e * bt_stride;
   const int h0 = blockIdx.y * hpb;
 
-  // this thread's two rows of the 16: (query, head), whether they exist, their position
-  int row_t[2], row_h[2], row_p[2];
-  bool row_ok[2];
+  // this thread's rows, two in every tile of 16: (query, head), whether they exist, their position
+  int row_t[MTL][2], row_h[MTL][2], row_p[MTL][2];
+  bool row_ok[MTL][2];
 #pragma unroll
-  for (int hh = 0; hh < 2; ++hh) {
-    const int rr = gid + 8 * hh, qi = rr / hpb, hd = h0 + rr % hpb;
-    row_ok[hh] = rr < tq * hpb && qi < nq && hd < H;
-    row_t[hh] = r0 + qbase + qi;
-    row_h[hh] = hd;
-    row_p[hh] = p_first + qi;
-  }
-  for (int i = threadIdx.x; i < 16 * W; i += kMmaWarps * 32) {
+  for (int rt = 0; rt < MTL; ++rt)
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int rr = 16 * rt + gid + 8 * hh, qi = rr / hpb, hd = h0 + rr % hpb;
+      row_ok[rt][hh] = rr < tq * hpb && qi < nq && hd < H;
+      row_t[rt][hh] = r0 + qbase + qi;
+      row_h[rt][hh] = hd;
+      row_p[rt][hh] = p_first + qi;
+    }
+  for (int i = threadIdx.x; i < ROWS * W; i += WARPS * 32) {
     const int rr = i / W, c = i - rr * W, qi = rr / hpb, hd = h0 + rr % hpb;
     const bool ok = rr < tq * hpb && qi < nq && hd < H;
     Qs[rr * LDW + c] = __float2bfloat16_rn(ok ? qa[((size_t)(r0 + qbase + qi) * H + hd) * W + c] : 0.f);
   }
 
-  const int tile0 = j_lo / kMmaKeys, n_tiles = p_last / kMmaKeys - tile0 + 1;
+  const int tile0 = j_lo / KEYS, n_tiles = p_last / KEYS - tile0 + 1;
   const int per = (n_tiles + num_splits - 1) / num_splits;
   const int t_begin = tile0 + split * per, t_end = min(tile0 + n_tiles, t_begin + per);
   const int chunks = W >> 3;   // 16-byte pieces of a row
   auto fetch = [&](int tile, int buf) {   // a warp takes every fourth row; its page is looked up once
-    __nv_bfloat16* dst = Ct + (size_t)buf * kMmaKeys * LDW;
+    __nv_bfloat16* dst = Ct + (size_t)buf * KEYS * LDW;
 #pragma unroll 2
-    for (int rr = warp; rr < kMmaKeys; rr += kMmaWarps) {
-      const int j = tile * kMmaKeys + rr;
+    for (int rr = warp; rr < KEYS; rr += WARPS) {
+      const int j = tile * KEYS + rr;
       const __nv_bfloat16* src = cache;
       bool ok = j >= j_lo && j <= p_last;
       if (ok) {
@@ -280,19 +285,22 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
     cp_async_commit();
   };
 
-  float m[2], l[2], acc[NPW][2][4];
+  float m[MTL][2], l[MTL][2], acc[MTL][NPW][2][4];
 #pragma unroll
-  for (int hh = 0; hh < 2; ++hh) {
-    const bool first = split == 0 && row_ok[hh];   // the sink: one term exp(sink) with no key and no value
-    m[hh] = first ? sink[row_h[hh]] : -CUDART_INF_F;
-    l[hh] = first ? 1.f : 0.f;
+  for (int rt = 0; rt < MTL; ++rt) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const bool first = split == 0 && row_ok[rt][hh];   // the sink: one term exp(sink) with no key and no value
+      m[rt][hh] = first ? sink[row_h[rt][hh]] : -CUDART_INF_F;
+      l[rt][hh] = first ? 1.f : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < NPW; ++i)
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) acc[rt][i][j][k] = 0.f;
   }
-#pragma unroll
-  for (int i = 0; i < NPW; ++i)
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int k = 0; k < 4; ++k) acc[i][j][k] = 0.f;
 
   const int n_pairs = R >> 4;
   if (t_begin < t_end) fetch(t_begin, 0);
@@ -305,87 +313,107 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
       cp_async_wait<0>();
     }
     __syncthreads();   // the tile (and, the first time, Q) is in shared memory for everyone
-    const __nv_bfloat16* C = Ct + (size_t)buf * kMmaKeys * LDW;
-    // ---- S = Q C^T for this warp's 8 keys
-    float sc[4] = {0.f, 0.f, 0.f, 0.f}, sc_odd[4] = {0.f, 0.f, 0.f, 0.f};   // two chains of products
+    const __nv_bfloat16* C = Ct + (size_t)buf * KEYS * LDW;
+    // ---- S = Q C^T for this warp's 8 keys (two chains of products per tile of rows)
+    float sc[MTL][4], sc_odd[MTL][4];
+#pragma unroll
+    for (int rt = 0; rt < MTL; ++rt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sc[rt][i] = sc_odd[rt][i] = 0.f;
     const uint32_t q_addr = smem_u32(Qs + (lane & 15) * LDW + (lane >> 4) * 8);
     const uint32_t k_addr = smem_u32(C + (8 * warp + (lane & 7)) * LDW + (lane >> 3) * 8);
     const int ksteps = W >> 4;
 #pragma unroll 3
     for (int ks = 0; ks < ksteps; ks += 2) {
-      uint32_t b[4], a[4], a2[4];
+      uint32_t b[4];
       ldmatrix_x4(b[0], b[1], b[2], b[3], k_addr + ks * 32);
-      ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + ks * 32);
-      if (ks + 1 < ksteps) ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], q_addr + (ks + 1) * 32);
-      mma_bf16_16816(sc, a, b[0], b[1]);
-      if (ks + 1 < ksteps) mma_bf16_16816(sc_odd, a2, b[2], b[3]);
-    }
+      const bool two = ks + 1 < ksteps;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) sc[i] += sc_odd[i];
-    // ---- softmax over the tile's 32 keys
-    const int jk = tile * kMmaKeys + 8 * warp + 2 * tig;
-    float mx[2];
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int lo = max(0, row_p[hh] - window + 1);
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int j = jk + c;
-        const bool seen = row_ok[hh] && j >= lo && j <= row_p[hh];
-        sc[2 * hh + c] = seen ? sc[2 * hh + c] * scale : -CUDART_INF_F;
+      for (int rt = 0; rt < MTL; ++rt) {
+        uint32_t a[4], a2[4];
+        ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + (rt * 16 * LDW) * 2 + ks * 32);
+        if (two) ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], q_addr + (rt * 16 * LDW) * 2 + (ks + 1) * 32);
+        mma_bf16_16816(sc[rt], a, b[0], b[1]);
+        if (two) mma_bf16_16816(sc_odd[rt], a2, b[2], b[3]);
       }
-      float v = fmaxf(sc[2 * hh], sc[2 * hh + 1]);
-      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
-      v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
-      mx[hh] = v;
-      if (tig == 0) red_max[warp * 16 + gid + 8 * hh] = v;
     }
+    // ---- softmax over the staged keys
+    const int jk = tile * KEYS + 8 * warp + 2 * tig;
+#pragma unroll
+    for (int rt = 0; rt < MTL; ++rt)
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const int lo = max(0, row_p[rt][hh] - window + 1);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int j = jk + c;
+          const bool seen = row_ok[rt][hh] && j >= lo && j <= row_p[rt][hh];
+          sc[rt][2 * hh + c] = seen ? (sc[rt][2 * hh + c] + sc_odd[rt][2 * hh + c]) * scale : -CUDART_INF_F;
+        }
+        float v = fmaxf(sc[rt][2 * hh], sc[rt][2 * hh + 1]);
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+        if (tig == 0) red_max[warp * ROWS + 16 * rt + gid + 8 * hh] = v;
+      }
     __syncthreads();
-    float corr[2];
+    float corr[MTL][2];
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      float mn = m[hh];
+    for (int rt = 0; rt < MTL; ++rt)
 #pragma unroll
-      for (int w = 0; w < kMmaWarps; ++w) mn = fmaxf(mn, red_max[w * 16 + gid + 8 * hh]);
-      const bool none = mn == -CUDART_INF_F;   // nothing seen so far (a piece without the sink)
-      corr[hh] = none ? 1.f : expf(m[hh] - mn);
-      m[hh] = mn;
-      const float p0 = none ? 0.f : expf(sc[2 * hh] - mn), p1 = none ? 0.f : expf(sc[2 * hh + 1] - mn);
-      float ps = p0 + p1;
-      ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-      ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-      if (tig == 0) red_sum[warp * 16 + gid + 8 * hh] = ps;
-      *reinterpret_cast<uint32_t*>(Ps + (gid + 8 * hh) * 40 + 8 * warp + 2 * tig) = pack_bf16(p0, p1);
-    }
+      for (int hh = 0; hh < 2; ++hh) {
+        const int rr = 16 * rt + gid + 8 * hh;
+        float mn = m[rt][hh];
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) mn = fmaxf(mn, red_max[w * ROWS + rr]);
+        const bool none = mn == -CUDART_INF_F;   // nothing seen so far (a piece without the sink)
+        corr[rt][hh] = none ? 1.f : expf(m[rt][hh] - mn);
+        m[rt][hh] = mn;
+        const float p0 = none ? 0.f : expf(sc[rt][2 * hh] - mn), p1 = none ? 0.f : expf(sc[rt][2 * hh + 1] - mn);
+        float ps = p0 + p1;
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        if (tig == 0) red_sum[warp * ROWS + rr] = ps;
+        *reinterpret_cast<uint32_t*>(Ps + rr * LDP + 8 * warp + 2 * tig) = pack_bf16(p0, p1);
+      }
     __syncthreads();
+    uint32_t pa[MTL][KEYS / 16][4];
+    const uint32_t p_addr = smem_u32(Ps + (lane & 15) * LDP + (lane >> 4) * 8);
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      float ps = 0.f;
+    for (int rt = 0; rt < MTL; ++rt) {
 #pragma unroll
-      for (int w = 0; w < kMmaWarps; ++w) ps += red_sum[w * 16 + gid + 8 * hh];
-      l[hh] = l[hh] * corr[hh] + ps;
+      for (int hh = 0; hh < 2; ++hh) {
+        const int rr = 16 * rt + gid + 8 * hh;
+        float ps = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) ps += red_sum[w * ROWS + rr];
+        l[rt][hh] = l[rt][hh] * corr[rt][hh] + ps;
+      }
+#pragma unroll
+      for (int ks = 0; ks < KEYS / 16; ++ks)
+        ldmatrix_x4(pa[rt][ks][0], pa[rt][ks][1], pa[rt][ks][2], pa[rt][ks][3], p_addr + rt * 16 * LDP * 2 + ks * 32);
     }
     // ---- O += P C for this warp's columns
-    uint32_t pa[2][4];
-    const uint32_t p_addr = smem_u32(Ps + (lane & 15) * 40 + (lane >> 4) * 8);
-    ldmatrix_x4(pa[0][0], pa[0][1], pa[0][2], pa[0][3], p_addr);
-    ldmatrix_x4(pa[1][0], pa[1][1], pa[1][2], pa[1][3], p_addr + 32);
     const uint32_t v_addr = smem_u32(C + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDW + (lane >> 4) * 8);
 #pragma unroll
     for (int i = 0; i < NPW; ++i) {
-      const int np = warp + kMmaWarps * i;
+      const int np = warp + WARPS * i;
       if (np < n_pairs) {
 #pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          acc[i][j][0] *= corr[0]; acc[i][j][1] *= corr[0];
-          acc[i][j][2] *= corr[1]; acc[i][j][3] *= corr[1];
-        }
+        for (int rt = 0; rt < MTL; ++rt)
 #pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
+          for (int j = 0; j < 2; ++j) {
+            acc[rt][i][j][0] *= corr[rt][0]; acc[rt][i][j][1] *= corr[rt][0];
+            acc[rt][i][j][2] *= corr[rt][1]; acc[rt][i][j][3] *= corr[rt][1];
+          }
+#pragma unroll
+        for (int ks = 0; ks < KEYS / 16; ++ks) {
           uint32_t b[4];
           ldmatrix_x4_trans(b[0], b[1], b[2], b[3], v_addr + (ks * 16 * LDW + np * 16) * 2);
-          mma_bf16_16816(acc[i][0], pa[ks], b[0], b[1]);
-          mma_bf16_16816(acc[i][1], pa[ks], b[2], b[3]);
+#pragma unroll
+          for (int rt = 0; rt < MTL; ++rt) {
+            mma_bf16_16816(acc[rt][i][0], pa[rt][ks], b[0], b[1]);
+            mma_bf16_16816(acc[rt][i][1], pa[rt][ks], b[2], b[3]);
+          }
         }
       }
     }
@@ -393,38 +421,40 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
   }
   // ---- the rows leave: finished (one piece) or as a piece of a row
 #pragma unroll
-  for (int hh = 0; hh < 2; ++hh) {
-    if (!row_ok[hh]) continue;
-    const size_t row = (size_t)row_t[hh] * H + row_h[hh];
-    if (num_splits == 1) {
-      const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)row_t[hh] * ldg + row_h[hh]])));
-      const float f = g / l[hh];
+  for (int rt = 0; rt < MTL; ++rt)
 #pragma unroll
-      for (int i = 0; i < NPW; ++i) {
-        const int np = warp + kMmaWarps * i;
-        if (np < n_pairs)
+    for (int hh = 0; hh < 2; ++hh) {
+      if (!row_ok[rt][hh]) continue;
+      const size_t row = (size_t)row_t[rt][hh] * H + row_h[rt][hh];
+      if (num_splits == 1) {
+        const float g = 1.0f / (1.0f + expf(-to_f32(gate[(size_t)row_t[rt][hh] * ldg + row_h[rt][hh]])));
+        const float f = g / l[rt][hh];
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
-            *reinterpret_cast<uint32_t*>(out + row * R + np * 16 + j * 8 + 2 * tig) =
-                pack_bf16(acc[i][j][2 * hh] * f, acc[i][j][2 * hh + 1] * f);
-      }
-    } else {
-      float* pa_out = part_acc + (row * num_splits + split) * R;
+        for (int i = 0; i < NPW; ++i) {
+          const int np = warp + WARPS * i;
+          if (np < n_pairs)
 #pragma unroll
-      for (int i = 0; i < NPW; ++i) {
-        const int np = warp + kMmaWarps * i;
-        if (np < n_pairs)
+            for (int j = 0; j < 2; ++j)
+              *reinterpret_cast<uint32_t*>(out + row * R + np * 16 + j * 8 + 2 * tig) =
+                  pack_bf16(acc[rt][i][j][2 * hh] * f, acc[rt][i][j][2 * hh + 1] * f);
+        }
+      } else {
+        float* pa_out = part_acc + (row * num_splits + split) * R;
 #pragma unroll
-          for (int j = 0; j < 2; ++j)
-            *reinterpret_cast<float2*>(pa_out + np * 16 + j * 8 + 2 * tig) =
-                make_float2(acc[i][j][2 * hh], acc[i][j][2 * hh + 1]);
-      }
-      if (warp == 0 && tig == 0) {
-        part_ml[(row * num_splits + split) * 2] = m[hh];
-        part_ml[(row * num_splits + split) * 2 + 1] = l[hh];
+        for (int i = 0; i < NPW; ++i) {
+          const int np = warp + WARPS * i;
+          if (np < n_pairs)
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+              *reinterpret_cast<float2*>(pa_out + np * 16 + j * 8 + 2 * tig) =
+                  make_float2(acc[rt][i][j][2 * hh], acc[rt][i][j][2 * hh + 1]);
+        }
+        if (warp == 0 && tig == 0) {
+          part_ml[(row * num_splits + split) * 2] = m[rt][hh];
+          part_ml[(row * num_splits + split) * 2 + 1] = l[rt][hh];
+        }
       }
     }
-  }
 }
 
 // out[t, h, :] = sigmoid(gate) * sum_s acc_s exp(m_s - M) / sum_s l_s exp(m_s - M); a block per (token, head),
@@ -462,10 +492,16 @@ latent_merge_kernel(const float* __restrict__ part_acc, const float* __restrict_
   }
   __syncthreads();
   const float* pa = part_acc + row * num_splits * R;
-  for (int c = threadIdx.x; c < R; c += kMergeThreads) {
-    float v = 0.f;
-    for (int s = 0; s < num_splits; ++s) v = fmaf(pa[(size_t)s * R + c], f[s], v);
-    out[row * R + c] = __float2bfloat16_rn(v);
+  const int c = blockIdx.y * kMergeThreads + threadIdx.x;   // a column a thread
+  if (c < R) {
+    float v0 = 0.f, v1 = 0.f;
+    int s = 0;
+    for (; s + 1 < num_splits; s += 2) {
+      v0 = fmaf(pa[(size_t)s * R + c], f[s], v0);
+      v1 = fmaf(pa[(size_t)(s + 1) * R + c], f[s + 1], v1);
+    }
+    if (s < num_splits) v0 = fmaf(pa[(size_t)s * R + c], f[s], v0);
+    out[row * R + c] = __float2bfloat16_rn(v0 + v1);
   }
 }
 
@@ -548,19 +584,21 @@ CCB_API int ccb_latent_attention(const float* qa, const void* cache, const float
 }
 
 namespace {
-template <int NPW>
+template <int NPW, int MTL, int WARPS>
 int launch_mma(const float* qa, const void* cache, const float* sink, const void* gate, int ldg, void* out,
                float* part_acc, float* part_ml, int num_splits, const int* cu_q, const int* pos0, const int* eot,
                const int* block_table, int bt_stride, int entry0, int n_entries, int max_q, int H, int R, int r,
                int page_size, int num_pages, int window, float scale, int* status, cudaStream_t stream) {
+  constexpr int ROWS = 16 * MTL, KEYS = 8 * WARPS;
   int hpb = 1;
-  while (hpb < 16 && hpb < H) hpb *= 2;
-  const int tq = 16 / hpb;
+  while (hpb < 16 && hpb < H) hpb *= 2;   // (with two tiles of rows a block still holds 16 heads at most)
+  const int tq = ROWS / hpb;
   const int W = R + r;
-  const size_t smem = (size_t)(16 + 2 * kMmaKeys) * (W + 8) * 2 + 16 * 40 * 2 + 64 + 2 * kMmaWarps * 16 * 4 + 64;
-  cudaFuncSetAttribute(latent_attention_mma_kernel<NPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const size_t smem = (size_t)(ROWS + 2 * KEYS) * (W + 8) * 2 + ROWS * (KEYS + 8) * 2 + 64 + 2 * WARPS * ROWS * 4 + 64;
+  cudaFuncSetAttribute(latent_attention_mma_kernel<NPW, MTL, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       (int)smem);
   dim3 grid((max_q + tq - 1) / tq, (H + hpb - 1) / hpb, n_entries * num_splits);
-  ccb_launch(latent_attention_mma_kernel<NPW>, grid, dim3(kMmaWarps * 32), smem, stream, qa,
+  ccb_launch(latent_attention_mma_kernel<NPW, MTL, WARPS>, grid, dim3(WARPS * 32), smem, stream, qa,
              (const __nv_bfloat16*)cache, sink, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, part_acc,
              part_ml, num_splits, cu_q, pos0, eot, block_table, bt_stride, entry0, H, R, r, page_size, num_pages,
              window, scale, hpb, status);
@@ -586,19 +624,28 @@ CCB_API int ccb_latent_attention_mma(const float* qa, const void* cache, const f
   if (!ccb_latent_attention_mma_fits(R, r) || H <= 0 || page_size <= 0 || window <= 0 || num_splits < 1 ||
       (long long)n_entries * num_splits > 65535 || num_splits > kMergeMaxSplits || (num_splits > 1 && (max_q != 1 || !part_acc || !part_ml)))
     return CCB_REFUSE_SIZE;
-  const int pairs_per_warp = ((R >> 4) + kMmaWarps - 1) / kMmaWarps;
+  // portions of prompts: 32 (query, head) rows and 8 warps a block; single tokens: 16 rows and 4 warps
+  const bool wide = max_q >= 16;
+  const int warps = wide ? 8 : kMmaWarps;
+  const int pairs_per_warp = ((R >> 4) + warps - 1) / warps;
   int rc;
-#define CCB_LMMA(NPW)                                                                                              \
-  rc = launch_mma<NPW>(qa, cache, sink, gate, ldg, out, part_acc, part_ml, num_splits, cu_q, pos0, entry_of_token, \
-                       block_table, bt_stride, entry0, n_entries, max_q, H, R, r, page_size, num_pages, window, scale, \
-                       status, stream)
-  if (pairs_per_warp <= 1) CCB_LMMA(1);
-  else if (pairs_per_warp <= 2) CCB_LMMA(2);
-  else if (pairs_per_warp <= 4) CCB_LMMA(4);
-  else CCB_LMMA(8);
+#define CCB_LMMA(NPW, MTL, WARPS)                                                                                  \
+  rc = launch_mma<NPW, MTL, WARPS>(qa, cache, sink, gate, ldg, out, part_acc, part_ml, num_splits, cu_q, pos0,     \
+                                   entry_of_token, block_table, bt_stride, entry0, n_entries, max_q, H, R, r,      \
+                                   page_size, num_pages, window, scale, status, stream)
+  if (wide) {
+    if (pairs_per_warp <= 1) CCB_LMMA(1, 2, 8);
+    else if (pairs_per_warp <= 2) CCB_LMMA(2, 2, 8);
+    else CCB_LMMA(4, 2, 8);
+  } else {
+    if (pairs_per_warp <= 1) CCB_LMMA(1, 1, 4);
+    else if (pairs_per_warp <= 2) CCB_LMMA(2, 1, 4);
+    else if (pairs_per_warp <= 4) CCB_LMMA(4, 1, 4);
+    else CCB_LMMA(8, 1, 4);
+  }
 #undef CCB_LMMA
   if (rc != 0 || num_splits == 1) return rc;
-  ccb_launch(latent_merge_kernel, dim3(n_entries * H), dim3(kMergeThreads), 0, stream, part_acc, part_ml, num_splits,
+  ccb_launch(latent_merge_kernel, dim3(n_entries * H, (R + kMergeThreads - 1) / kMergeThreads), dim3(kMergeThreads), 0, stream, part_acc, part_ml, num_splits,
              (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, entry_of_token, entry0, H, R);
   return ccb_launch_status();
 }
