@@ -460,6 +460,9 @@ CCB_API int ccb_moe_grouped(const void* A, int lda, const int* src_row, const vo
              0, stream, (const __nv_bfloat16*)A, lda, src_row, (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, \
              row_w, tile_e, tile_r0, tile_n, N, K)
   if (BM == 16) { if (mode == 0) CCB_GROUPED(1, 1, 4, 0); else CCB_GROUPED(1, 1, 4, 1); }
+  // many rows: 128 columns a block and one step of k in flight behind the one in use.  Measured and not kept
+  // (2,048 tokens, 32 experts of 1024 x 2048, 4 chosen): 64 columns a block with two steps in flight 0.79 against
+  // 0.63 ms for the whole part, 64 columns with one step 0.66 ms
   else if (BM == 32) { if (mode == 0) CCB_GROUPED(2, 4, 1, 0); else CCB_GROUPED(2, 4, 1, 1); }
   else if (BM == 64) { if (mode == 0) CCB_GROUPED(4, 4, 1, 0); else CCB_GROUPED(4, 4, 1, 1); }
   else return CCB_REFUSE_SIZE;
