@@ -37,6 +37,7 @@ GROUPS = {
         "linear_attention.cu",
         "latent_attention.cu",
         "moe.cu",
+        "moe_tcgen05.cu",
         "attention_generic.cu",
         "attention_split.cu",
         "attention_decode_mma.cu",

@@ -96,6 +96,9 @@ _SIGNATURES = {
                      c_void_p, c_void_p, c_void_p],
     "ccb_moe_grouped": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "ccb_moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "ccb_moe_grouped_tc": [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                           c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
     "ccb_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_scaled_residual": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_void_p],
     "ccb_concat_cast": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -626,6 +629,31 @@ def moe_grouped(c, a, src_row, w, w_expert_stride: int, row_w, tile_e, tile_r0, 
     _check(lib().ccb_moe_grouped(_p(a), a.stride(0), _p(src_row), _p(w), w.stride(0), int(w_expert_stride), _p(c),
                                  c.stride(0), _p(row_w), _p(tile_e), _p(tile_r0), _p(tile_n), tile_e.numel(), N, K, BM,
                                  mode, _dt(a), _stream()), "moe_grouped")
+
+
+MOE_TC_ROWS = 128   # rows of a tile of the tcgen05 grouped product
+
+
+def moe_gather_rows(out, x, src_row) -> None:
+    """out[pos] = x[src_row[pos]]: the tokens of the sorted (token, choice) pairs as contiguous bfloat16 rows."""
+    _cuda(out, src_row)
+    rows, width = out.shape
+    assert x.stride(1) == 1 and x.shape[1] == width and out.dtype == x.dtype == torch.bfloat16
+    assert src_row.dtype == torch.int32 and src_row.numel() >= rows
+    _check(lib().ccb_moe_gather_rows(_p(out), _p(x), _p(src_row), rows, width, x.stride(0), _stream()),
+           "moe_gather_rows")
+
+
+def moe_grouped_tc(c, a, w, row_w, tile_e, tile_r0, tile_n, N: int, K: int, F: int, mode: int, status=None) -> None:
+    """``moe_grouped`` on tcgen05 tensor cores for tiles of MOE_TC_ROWS sorted rows (bfloat16).  ``a`` holds the
+    sorted rows themselves.  mode 0: ``w`` = all first matrices stacked [E F, K], c bfloat16 [rows, F] =
+    relu(a W_e^T)^2 * row_w;  mode 1: ``w`` = all second matrices side by side [N, E F] (K = F), c float."""
+    _cuda(a, w, row_w, tile_e, tile_r0, tile_n, status)
+    assert a.dtype == w.dtype == torch.bfloat16 and c.dtype == (torch.bfloat16 if mode == 0 else torch.float32)
+    assert a.shape[1] == K and c.shape == (a.shape[0], N) and c.is_contiguous()
+    _check(lib().ccb_moe_grouped_tc(_p(a), a.stride(0), a.shape[0], _p(w), w.stride(0), w.shape[0], w.shape[1], _p(c),
+                                    c.stride(0), _p(row_w), _p(tile_e), _p(tile_r0), _p(tile_n), tile_e.numel(), N, K,
+                                    F, mode, _p(status), _stream()), "moe_grouped_tc")
 
 
 def moe_combine(out, rows, pair_pos, shared, top: int) -> None:

@@ -14,7 +14,8 @@ Two forms, chosen by size (``sparse=`` forces one):
   each expert's columns by the token's weight for it (zero where it was not chosen), and ONE product with all
   second matrices side by side, which also adds the experts up;
 * sparse: the (token, choice) pairs are sorted by expert and only the chosen experts run, as two grouped
-  products over tiles of one expert's rows (``csrc/moe.cu``); the shared expert is two ordinary products; a last
+  products over tiles of one expert's rows (``csrc/moe.cu``: mma.sync with operands straight from global memory
+  for few rows an expert; ``csrc/moe_tcgen05.cu``: tcgen05 with TMA for many); the shared expert is two ordinary products; a last
   kernel adds each token's rows up in the order of its choices.  A decode step then reads the chosen experts'
   weights and no others.
 
@@ -33,6 +34,7 @@ class MixtureOfExperts(FeedForward):
     # from this many weights of the routed experts on, the sparse form runs (measured on B200: below, the dense
     # form's two products cost less than the sparse form's extra launches)
     SPARSE_MIN_WEIGHTS = 1 << 22
+    TC_MIN_ROWS_PER_EXPERT = 64   # (token, choice) pairs per expert from which the tcgen05 grouped product runs
 
     def __init__(self, hidden: int, experts: int, top: int, expert_ff: int, names: dict, groups: int = 1,
                  keep: int = 1, shared_ff: int = 0, activation: str = "relu2", sparse=None):
@@ -97,8 +99,12 @@ class MixtureOfExperts(FeedForward):
         i32, f32 = torch.int32, torch.float32
         idx, wts, _ = self.route(x, T)
         pairs, max_pairs = T * top, rt.max_tokens * top
-        # rows per tile: as many as an expert gets on average, so that its weights are read once per 16 to 64 rows
+        # rows per tile: as many as an expert gets on average, so that its weights are read once per 16 to 64 rows;
+        # from 64 rows an expert on, tiles of 128 rows on tcgen05 (bfloat16)
+        tc = rt.dtype == torch.bfloat16 and pairs >= self.TC_MIN_ROWS_PER_EXPERT * E
         BM = 16 if (rt.dtype == f32 or pairs <= 16 * E) else (32 if pairs <= 32 * E else 64)
+        if tc:
+            BM = kernels.MOE_TC_ROWS
         n_tiles = kernels.moe_max_tiles(pairs, E, BM)
         cap = kernels.moe_max_tiles(max_pairs, E, 16)
         src_row = rt.scratch.get("moe_src_row", (max_pairs,), i32)
@@ -107,9 +113,15 @@ class MixtureOfExperts(FeedForward):
         tiles = [rt.scratch.get(f"moe_tile{k}", (cap,), i32)[:n_tiles] for k in range(3)]
         kernels.moe_sort(idx, wts, E, BM, src_row, row_w, pair_pos, *tiles)
         act = rt.scratch.get("moe_act_rows", (max_pairs, F), rt.dtype)[:pairs]
-        kernels.moe_grouped(act, x, src_row, self.w_up, F * self.w_up.stride(0), row_w, *tiles, F, D, BM, 0)
         rows = rt.scratch.get("moe_out_rows", (max_pairs, D), f32)[:pairs]
-        kernels.moe_grouped(rows, act, None, self.w_down, F, row_w, *tiles, D, F, BM, 1)
+        if tc:
+            xs = rt.scratch.get("moe_x_sorted", (max_pairs, D), rt.dtype)[:pairs]
+            kernels.moe_gather_rows(xs, x, src_row)
+            kernels.moe_grouped_tc(act, xs, self.w_up, row_w, *tiles, F, D, F, 0, status=rt.status)
+            kernels.moe_grouped_tc(rows, act, self.w_down, row_w, *tiles, D, F, F, 1, status=rt.status)
+        else:
+            kernels.moe_grouped(act, x, src_row, self.w_up, F * self.w_up.stride(0), row_w, *tiles, F, D, BM, 0)
+            kernels.moe_grouped(rows, act, None, self.w_down, F, row_w, *tiles, D, F, BM, 1)
         shared = None
         if self.SF:
             sa = rt.scratch.get("moe_shared_act", (rt.max_tokens, self.SF), rt.dtype)[:T]
