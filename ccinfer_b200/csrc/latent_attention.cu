@@ -206,11 +206,12 @@ latent_attention_kernel(const float* __restrict__ qa, const T* __restrict__ cach
 // reads fall into different banks.
 constexpr int kMmaWarps = 4;   // of a block of single tokens
 
-// MTL: tiles of 16 rows a block; WARPS: its warps, each with 8 of the 8 * WARPS keys staged at a time.  Single
-// tokens: 16 rows, 4 warps, 32 keys (two blocks an SM).  Portions of prompts: 32 rows, 8 warps, 64 keys (one
-// block an SM): twice the queries share every staged key and the block meets at its barriers half as often.
+// MTL: tiles of 16 rows a block; WARPS: the warps of one tile of rows, each with 8 of the 8 * WARPS keys staged at
+// a time (a block has MTL * WARPS warps: warp (rt, wk) owns the tile of rows rt and the keys / columns of wk).
+// Single tokens: 16 rows, 4 warps, 32 keys (two blocks an SM).  Portions of prompts: 32 rows, 16 warps, 64 keys
+// (one block an SM): twice the queries share every staged key and the block meets at its barriers half as often.
 template <int NPW, int MTL, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * MTL * 32)
 latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* __restrict__ cache,
                             const float* __restrict__ sink, const __nv_bfloat16* __restrict__ gate, int ldg,
                             __nv_bfloat16* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
@@ -233,6 +234,8 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
   const int qbase = blockIdx.x * tq;
   if (qbase >= n || entry_of_token[r0 + qbase] < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  constexpr int NW = WARPS * MTL;
+  const int wk = warp % WARPS, rt0 = warp / WARPS;
   const int nq = min(tq, n - qbase);
   const int p_first = pos0[e] + qbase, p_last = p_first + nq - 1;
   const int j_lo = max(0, p_first - window + 1);
@@ -240,19 +243,19 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
   const int h0 = blockIdx.y * hpb;
 
   // this thread's rows, two in every tile of 16: (query, head), whether they exist, their position
-  int row_t[MTL][2], row_h[MTL][2], row_p[MTL][2];
-  bool row_ok[MTL][2];
+  int row_t[1][2], row_h[1][2], row_p[1][2];
+  bool row_ok[1][2];
 #pragma unroll
-  for (int rt = 0; rt < MTL; ++rt)
+  for (int rt = 0; rt < 1; ++rt)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      const int rr = 16 * rt + gid + 8 * hh, qi = rr / hpb, hd = h0 + rr % hpb;
+      const int rr = 16 * (rt0 + rt) + gid + 8 * hh, qi = rr / hpb, hd = h0 + rr % hpb;
       row_ok[rt][hh] = rr < tq * hpb && qi < nq && hd < H;
       row_t[rt][hh] = r0 + qbase + qi;
       row_h[rt][hh] = hd;
       row_p[rt][hh] = p_first + qi;
     }
-  for (int i = threadIdx.x; i < ROWS * W; i += WARPS * 32) {
+  for (int i = threadIdx.x; i < ROWS * W; i += NW * 32) {
     const int rr = i / W, c = i - rr * W, qi = rr / hpb, hd = h0 + rr % hpb;
     const bool ok = rr < tq * hpb && qi < nq && hd < H;
     Qs[rr * LDW + c] = __float2bfloat16_rn(ok ? qa[((size_t)(r0 + qbase + qi) * H + hd) * W + c] : 0.f);
@@ -265,7 +268,7 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
   auto fetch = [&](int tile, int buf) {   // a warp takes every fourth row; its page is looked up once
     __nv_bfloat16* dst = Ct + (size_t)buf * KEYS * LDW;
 #pragma unroll 2
-    for (int rr = warp; rr < KEYS; rr += WARPS) {
+    for (int rr = warp; rr < KEYS; rr += NW) {
       const int j = tile * KEYS + rr;
       const __nv_bfloat16* src = cache;
       bool ok = j >= j_lo && j <= p_last;
@@ -285,9 +288,9 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
     cp_async_commit();
   };
 
-  float m[MTL][2], l[MTL][2], acc[MTL][NPW][2][4];
+  float m[1][2], l[1][2], acc[1][NPW][2][4];
 #pragma unroll
-  for (int rt = 0; rt < MTL; ++rt) {
+  for (int rt = 0; rt < 1; ++rt) {
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       const bool first = split == 0 && row_ok[rt][hh];   // the sink: one term exp(sink) with no key and no value
@@ -315,13 +318,13 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
     __syncthreads();   // the tile (and, the first time, Q) is in shared memory for everyone
     const __nv_bfloat16* C = Ct + (size_t)buf * KEYS * LDW;
     // ---- S = Q C^T for this warp's 8 keys (two chains of products per tile of rows)
-    float sc[MTL][4], sc_odd[MTL][4];
+    float sc[1][4], sc_odd[1][4];
 #pragma unroll
-    for (int rt = 0; rt < MTL; ++rt)
+    for (int rt = 0; rt < 1; ++rt)
 #pragma unroll
       for (int i = 0; i < 4; ++i) sc[rt][i] = sc_odd[rt][i] = 0.f;
     const uint32_t q_addr = smem_u32(Qs + (lane & 15) * LDW + (lane >> 4) * 8);
-    const uint32_t k_addr = smem_u32(C + (8 * warp + (lane & 7)) * LDW + (lane >> 3) * 8);
+    const uint32_t k_addr = smem_u32(C + (8 * wk + (lane & 7)) * LDW + (lane >> 3) * 8);
     const int ksteps = W >> 4;
 #pragma unroll 3
     for (int ks = 0; ks < ksteps; ks += 2) {
@@ -329,18 +332,18 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
       ldmatrix_x4(b[0], b[1], b[2], b[3], k_addr + ks * 32);
       const bool two = ks + 1 < ksteps;
 #pragma unroll
-      for (int rt = 0; rt < MTL; ++rt) {
+      for (int rt = 0; rt < 1; ++rt) {
         uint32_t a[4], a2[4];
-        ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + (rt * 16 * LDW) * 2 + ks * 32);
-        if (two) ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], q_addr + (rt * 16 * LDW) * 2 + (ks + 1) * 32);
+        ldmatrix_x4(a[0], a[1], a[2], a[3], q_addr + ((rt0 + rt) * 16 * LDW) * 2 + ks * 32);
+        if (two) ldmatrix_x4(a2[0], a2[1], a2[2], a2[3], q_addr + ((rt0 + rt) * 16 * LDW) * 2 + (ks + 1) * 32);
         mma_bf16_16816(sc[rt], a, b[0], b[1]);
         if (two) mma_bf16_16816(sc_odd[rt], a2, b[2], b[3]);
       }
     }
     // ---- softmax over the staged keys
-    const int jk = tile * KEYS + 8 * warp + 2 * tig;
+    const int jk = tile * KEYS + 8 * wk + 2 * tig;
 #pragma unroll
-    for (int rt = 0; rt < MTL; ++rt)
+    for (int rt = 0; rt < 1; ++rt)
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         const int lo = max(0, row_p[rt][hh] - window + 1);
@@ -353,15 +356,15 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
         float v = fmaxf(sc[rt][2 * hh], sc[rt][2 * hh + 1]);
         v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
         v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
-        if (tig == 0) red_max[warp * ROWS + 16 * rt + gid + 8 * hh] = v;
+        if (tig == 0) red_max[wk * ROWS + 16 * (rt0 + rt) + gid + 8 * hh] = v;
       }
     __syncthreads();
-    float corr[MTL][2];
+    float corr[1][2];
 #pragma unroll
-    for (int rt = 0; rt < MTL; ++rt)
+    for (int rt = 0; rt < 1; ++rt)
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        const int rr = 16 * rt + gid + 8 * hh;
+        const int rr = 16 * (rt0 + rt) + gid + 8 * hh;
         float mn = m[rt][hh];
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) mn = fmaxf(mn, red_max[w * ROWS + rr]);
@@ -372,17 +375,17 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
         float ps = p0 + p1;
         ps += __shfl_xor_sync(0xffffffffu, ps, 1);
         ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-        if (tig == 0) red_sum[warp * ROWS + rr] = ps;
-        *reinterpret_cast<uint32_t*>(Ps + rr * LDP + 8 * warp + 2 * tig) = pack_bf16(p0, p1);
+        if (tig == 0) red_sum[wk * ROWS + rr] = ps;
+        *reinterpret_cast<uint32_t*>(Ps + rr * LDP + 8 * wk + 2 * tig) = pack_bf16(p0, p1);
       }
     __syncthreads();
-    uint32_t pa[MTL][KEYS / 16][4];
+    uint32_t pa[1][KEYS / 16][4];
     const uint32_t p_addr = smem_u32(Ps + (lane & 15) * LDP + (lane >> 4) * 8);
 #pragma unroll
-    for (int rt = 0; rt < MTL; ++rt) {
+    for (int rt = 0; rt < 1; ++rt) {
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
-        const int rr = 16 * rt + gid + 8 * hh;
+        const int rr = 16 * (rt0 + rt) + gid + 8 * hh;
         float ps = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) ps += red_sum[w * ROWS + rr];
@@ -390,16 +393,16 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
       }
 #pragma unroll
       for (int ks = 0; ks < KEYS / 16; ++ks)
-        ldmatrix_x4(pa[rt][ks][0], pa[rt][ks][1], pa[rt][ks][2], pa[rt][ks][3], p_addr + rt * 16 * LDP * 2 + ks * 32);
+        ldmatrix_x4(pa[rt][ks][0], pa[rt][ks][1], pa[rt][ks][2], pa[rt][ks][3], p_addr + (rt0 + rt) * 16 * LDP * 2 + ks * 32);
     }
     // ---- O += P C for this warp's columns
     const uint32_t v_addr = smem_u32(C + ((lane & 7) + ((lane >> 3) & 1) * 8) * LDW + (lane >> 4) * 8);
 #pragma unroll
     for (int i = 0; i < NPW; ++i) {
-      const int np = warp + WARPS * i;
+      const int np = wk + WARPS * i;
       if (np < n_pairs) {
 #pragma unroll
-        for (int rt = 0; rt < MTL; ++rt)
+        for (int rt = 0; rt < 1; ++rt)
 #pragma unroll
           for (int j = 0; j < 2; ++j) {
             acc[rt][i][j][0] *= corr[rt][0]; acc[rt][i][j][1] *= corr[rt][0];
@@ -410,7 +413,7 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
           uint32_t b[4];
           ldmatrix_x4_trans(b[0], b[1], b[2], b[3], v_addr + (ks * 16 * LDW + np * 16) * 2);
 #pragma unroll
-          for (int rt = 0; rt < MTL; ++rt) {
+          for (int rt = 0; rt < 1; ++rt) {
             mma_bf16_16816(acc[rt][i][0], pa[rt][ks], b[0], b[1]);
             mma_bf16_16816(acc[rt][i][1], pa[rt][ks], b[2], b[3]);
           }
@@ -421,7 +424,7 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
   }
   // ---- the rows leave: finished (one piece) or as a piece of a row
 #pragma unroll
-  for (int rt = 0; rt < MTL; ++rt)
+  for (int rt = 0; rt < 1; ++rt)
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
       if (!row_ok[rt][hh]) continue;
@@ -431,7 +434,7 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
         const float f = g / l[rt][hh];
 #pragma unroll
         for (int i = 0; i < NPW; ++i) {
-          const int np = warp + WARPS * i;
+          const int np = wk + WARPS * i;
           if (np < n_pairs)
 #pragma unroll
             for (int j = 0; j < 2; ++j)
@@ -442,14 +445,14 @@ latent_attention_mma_kernel(const float* __restrict__ qa, const __nv_bfloat16* _
         float* pa_out = part_acc + (row * num_splits + split) * R;
 #pragma unroll
         for (int i = 0; i < NPW; ++i) {
-          const int np = warp + WARPS * i;
+          const int np = wk + WARPS * i;
           if (np < n_pairs)
 #pragma unroll
             for (int j = 0; j < 2; ++j)
               *reinterpret_cast<float2*>(pa_out + np * 16 + j * 8 + 2 * tig) =
                   make_float2(acc[rt][i][j][2 * hh], acc[rt][i][j][2 * hh + 1]);
         }
-        if (warp == 0 && tig == 0) {
+        if (wk == 0 && tig == 0) {
           part_ml[(row * num_splits + split) * 2] = m[rt][hh];
           part_ml[(row * num_splits + split) * 2 + 1] = l[rt][hh];
         }
@@ -598,7 +601,7 @@ int launch_mma(const float* qa, const void* cache, const float* sink, const void
   cudaFuncSetAttribute(latent_attention_mma_kernel<NPW, MTL, WARPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                        (int)smem);
   dim3 grid((max_q + tq - 1) / tq, (H + hpb - 1) / hpb, n_entries * num_splits);
-  ccb_launch(latent_attention_mma_kernel<NPW, MTL, WARPS>, grid, dim3(WARPS * 32), smem, stream, qa,
+  ccb_launch(latent_attention_mma_kernel<NPW, MTL, WARPS>, grid, dim3(WARPS * MTL * 32), smem, stream, qa,
              (const __nv_bfloat16*)cache, sink, (const __nv_bfloat16*)gate, ldg, (__nv_bfloat16*)out, part_acc,
              part_ml, num_splits, cu_q, pos0, eot, block_table, bt_stride, entry0, H, R, r, page_size, num_pages,
              window, scale, hpb, status);
@@ -624,7 +627,7 @@ CCB_API int ccb_latent_attention_mma(const float* qa, const void* cache, const f
   if (!ccb_latent_attention_mma_fits(R, r) || H <= 0 || page_size <= 0 || window <= 0 || num_splits < 1 ||
       (long long)n_entries * num_splits > 65535 || num_splits > kMergeMaxSplits || (num_splits > 1 && (max_q != 1 || !part_acc || !part_ml)))
     return CCB_REFUSE_SIZE;
-  // portions of prompts: 32 (query, head) rows and 8 warps a block; single tokens: 16 rows and 4 warps
+  // portions of prompts: 32 (query, head) rows and 16 warps a block; single tokens: 16 rows and 4 warps
   const bool wide = max_q >= 16;
   const int warps = wide ? 8 : kMmaWarps;
   const int pairs_per_warp = ((R >> 4) + warps - 1) / warps;
