@@ -234,6 +234,16 @@ CONFIGS = {
                  (gla(4, 64, 64, 16.0), moe_cfg(16, 4, 64, groups=(4, 2), shared=64)),
                  (latent(2, 64, 32, 64, 128, 33, 0.1, dims=16), moe_cfg(4, 2, 128))],
                 loop=(1, 2, 2), side=16), {1: 16}, 16),
+    # twelve heads (a block's 16 rows are not all used), a latent size of six 16-column pairs, every layer looped,
+    # every expert of a layer chosen, a tau below one
+    "D": (model(300, 192, 1e-5,
+                [(gla(5, 40, 56, 0.7), moe_cfg(12, 3, 48, groups=(3, 2), shared=80)),
+                 (latent(12, 64, 32, 40, 96, 100, 0.12, base=3000.0), moe_cfg(4, 4, 16, groups=(2, 2)))],
+                loop=(0, 2, 2), side=12), {0: 7}, 16),
+    # two heads over a latent size of 256, a window shorter than a page, long keys in the recurrence
+    "E": (model(150, 320, 1e-6,
+                [(latent(2, 48, 64, 128, 256, 8, 0.2, dims=32), moe_cfg(8, 2, 40, shared=24)),
+                 (gla(2, 128, 32, 30.0), moe_cfg(3, 1, 64))]), {1: 24}, 16),
 }
 
 

@@ -353,9 +353,10 @@ def test_latent_attention_mixer_alone(dtype, H, d, r, dims, dv, R, window, page,
 # ---------------------------------------------------------------------------------------------
 # GPU: whole models under every cutting
 # ---------------------------------------------------------------------------------------------
-# prompt lengths just below, at and just above the windows (24, 17; 9, 30; 70, 33) and the pages' borders (8; 4; 16)
+# prompt lengths just below, at and just above the windows (24, 17; 9, 30; 70, 33; 100; 8) and the pages' borders
 LENGTHS = {"A": [1, 2, 16, 17, 18, 23, 24, 25, 26, 60, 97], "B": [1, 3, 8, 9, 10, 11, 29, 30, 31, 32, 75],
-           "C": [2, 32, 33, 34, 35, 69, 70, 71, 72, 150]}
+           "C": [2, 32, 33, 34, 35, 69, 70, 71, 72, 150], "D": [1, 15, 16, 17, 99, 100, 101, 102, 130],
+           "E": [1, 7, 8, 9, 10, 16, 17, 40, 90]}
 
 
 @pytest.fixture(scope="module")
