@@ -347,6 +347,99 @@ moe_grouped_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int*
     }
 }
 
+// Few rows an expert (tiles of 16, a decode step): the product is a stream of the chosen experts' matrices, and
+// what counts is bytes in flight.  A block takes 8 columns of a tile; its four warps take a quarter of k each
+// (four steps of 32 loaded at once, the next four on their way) and add their parts up through shared memory.
+// N / 8 blocks a tile instead of N / 32: every SM holds several, each warp with 2 KB in flight.
+template <int MODE>
+__global__ void __launch_bounds__(128)
+moe_grouped_rows16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ src_row,
+                          const __nv_bfloat16* __restrict__ W, int ldw, long long w_expert_stride,
+                          void* __restrict__ Cout, int ldc, const float* __restrict__ row_w,
+                          const int* __restrict__ tile_e, const int* __restrict__ tile_r0,
+                          const int* __restrict__ tile_n, int N, int K) {
+  ccb::pdl_begin();
+  constexpr int DEPTH = 4;
+  __shared__ float red[3][32][4];
+  const int tile = blockIdx.y;
+  const int n_rows = tile_n[tile];
+  if (n_rows <= 0) return;
+  const int e = tile_e[tile], r0 = tile_r0[tile];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int gid = lane >> 2, tig = lane & 3;
+  const int n_base = blockIdx.x * 8;
+  const int col = n_base + gid;
+  const bool wok = col < N;
+  const __nv_bfloat16* wrow = W + (size_t)e * w_expert_stride + (size_t)(wok ? col : 0) * ldw;
+  const __nv_bfloat16* arow[2];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    int r = hh * 8 + gid;
+    if (r >= n_rows) r = n_rows - 1;
+    const int g = r0 + r;
+    arow[hh] = A + (size_t)(src_row ? src_row[g] : g) * lda;
+  }
+  // this warp's share of k: whole steps of 32
+  const int steps = (K + 31) >> 5, per = (steps + 3) >> 2;
+  const int k_begin = warp * per * 32, k_end = min(K, (warp + 1) * per * 32);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  uint4 a[DEPTH][2], b[DEPTH];
+  auto load = [&](int k0) {
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      const int k = k0 + 32 * d + 8 * tig;
+      const bool ok = k < k_end;
+      a[d][0] = ld16_or_zero(arow[0] + k, ok);
+      a[d][1] = ld16_or_zero(arow[1] + k, ok);
+      b[d] = ld16_or_zero(wrow + k, ok && wok);
+    }
+  };
+  if (k_begin < k_end) load(k_begin);
+  for (int k0 = k_begin; k0 < k_end; k0 += 32 * DEPTH) {
+    uint4 ca[DEPTH][2], cb[DEPTH];
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) ca[d][0] = a[d][0], ca[d][1] = a[d][1], cb[d] = b[d];
+    if (k0 + 32 * DEPTH < k_end) load(k0 + 32 * DEPTH);
+#pragma unroll
+    for (int d = 0; d < DEPTH; ++d) {
+      const uint32_t f0[4] = {ca[d][0].x, ca[d][1].x, ca[d][0].y, ca[d][1].y};
+      const uint32_t f1[4] = {ca[d][0].z, ca[d][1].z, ca[d][0].w, ca[d][1].w};
+      mma_bf16_16816(acc, f0, cb[d].x, cb[d].y);
+      mma_bf16_16816(acc, f1, cb[d].z, cb[d].w);
+    }
+  }
+  if (warp > 0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[warp - 1][lane][i] = acc[i];
+  }
+  __syncthreads();
+  if (warp > 0) return;
+#pragma unroll
+  for (int w = 0; w < 3; ++w)   // the quarters of k are added in their order
+#pragma unroll
+    for (int i = 0; i < 4; ++i) acc[i] += red[w][lane][i];
+#pragma unroll
+  for (int hh = 0; hh < 2; ++hh) {
+    const int r = hh * 8 + gid;
+    if (r >= n_rows) continue;
+    const size_t g = (size_t)(r0 + r);
+    const int c0 = n_base + 2 * tig;
+    float v0 = acc[hh * 2], v1 = acc[hh * 2 + 1];
+    if (MODE == 0) {
+      const float wr = row_w[g];
+      v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f);
+      v0 = v0 * v0 * wr; v1 = v1 * v1 * wr;
+      __nv_bfloat16* c = (__nv_bfloat16*)Cout + g * ldc + c0;
+      if (c0 < N) c[0] = __float2bfloat16_rn(v0);
+      if (c0 + 1 < N) c[1] = __float2bfloat16_rn(v1);
+    } else {
+      float* c = (float*)Cout + g * ldc + c0;
+      if (c0 < N) c[0] = v0;
+      if (c0 + 1 < N) c[1] = v1;
+    }
+  }
+}
+
 // The float path: a tile of up to 16 rows x 128 columns a block, a column a thread, A staged in shared memory.
 template <int MODE>
 __global__ void __launch_bounds__(128)
@@ -421,7 +514,8 @@ CCB_API int ccb_moe_sort(const int* idx, const float* wts, int pairs, int top, i
                          int* src_row, float* row_w, int* pair_pos, int* tile_e, int* tile_r0, int* tile_n,
                          cudaStream_t stream) {
   if (pairs <= 0) return 0;
-  if (E <= 0 || top <= 0 || BM <= 0 || max_tiles < (pairs + BM - 1) / BM + E) return CCB_REFUSE_SIZE;
+  // (every tile holds a pair, so there are never more tiles than pairs)
+  if (E <= 0 || top <= 0 || BM <= 0 || max_tiles < min(pairs, (pairs + BM - 1) / BM + E)) return CCB_REFUSE_SIZE;
   const size_t smem = (size_t)(4 * E + 2) * sizeof(int);
   if (smem > 96 * 1024) return CCB_REFUSE_SIZE;
   cudaFuncSetAttribute(moe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -453,13 +547,20 @@ CCB_API int ccb_moe_grouped(const void* A, int lda, const int* src_row, const vo
   if (K % 8 || lda % 8 || ldw % 8 || w_expert_stride % 8 || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(W) & 15))
     return CCB_REFUSE_SIZE;
-  // few rows an expert (tiles of 16): a block takes 32 columns only and loads four steps of k at once, so that
-  // a decode step has enough blocks and bytes in flight to stream the chosen experts' weights
+  // few rows an expert (tiles of 16): moe_grouped_rows16_kernel, 8 columns a block and k cut over its warps
 #define CCB_GROUPED(MT, NT, DEPTH, MODE)                                                                          \
   ccb_launch(moe_grouped_bf16_kernel<MT, NT, DEPTH, MODE>, dim3(max_tiles, (N + 32 * NT - 1) / (32 * NT)), dim3(128), \
              0, stream, (const __nv_bfloat16*)A, lda, src_row, (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, \
              row_w, tile_e, tile_r0, tile_n, N, K)
-  if (BM == 16) { if (mode == 0) CCB_GROUPED(1, 1, 4, 0); else CCB_GROUPED(1, 1, 4, 1); }
+  if (BM == 16) {
+    dim3 grid16((N + 7) / 8, max_tiles);   // the tiles that hold rows come first in the list, and so do their blocks
+    if (mode == 0)
+      ccb_launch(moe_grouped_rows16_kernel<0>, grid16, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row,
+                 (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
+    else
+      ccb_launch(moe_grouped_rows16_kernel<1>, grid16, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row,
+                 (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
+  }
   // many rows: 128 columns a block and one step of k in flight behind the one in use.  Measured and not kept
   // (2,048 tokens, 32 experts of 1024 x 2048, 4 chosen): 64 columns a block with two steps in flight 0.79 against
   // 0.63 ms for the whole part, 64 columns with one step 0.66 ms

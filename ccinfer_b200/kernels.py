@@ -601,7 +601,7 @@ def moe_dense_act(act, dense_w, E: int, F: int, shared: int) -> None:
 
 def moe_max_tiles(pairs: int, E: int, BM: int) -> int:
     """Tiles of BM rows that the sorted (token, choice) pairs of a step can need at most."""
-    return -(-pairs // BM) + E
+    return min(pairs, -(-pairs // BM) + E)   # (every tile holds a pair)
 
 
 def moe_sort(idx, wts, E: int, BM: int, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n) -> None:
