@@ -158,11 +158,12 @@ CCB_API int ccb_moe_dense_act(void* act, int ld, const float* dense_w, int rows,
 //
 //   moe_sort       one block: counts per expert, their prefix sums, the place of every pair among its expert's
 //                  rows (pair_pos), the token and weight of every sorted row, and the list of tiles
-//   moe_grouped    C[row, :] = A[src(row), :] W_e^T for the rows of every tile, W_e the tile's expert:
+//   moe_grouped    C[row, :] = A[src(row), :] W_e^T for the rows of every tile of 16, W_e the tile's expert:
 //                  bfloat16 on mma.sync m16n8k16 with float sums.  Both operands go from global memory straight
 //                  into the fragments: a thread loads 8 neighbouring k of its rows with ONE 16-byte access and
 //                  uses them as two k-pairs of two products.  Which k a fragment's place stands for does not
-//                  matter as long as A and B agree, and they do: both load the same way.
+//                  matter as long as A and B agree, and they do: both load the same way.  (Tiles of 128 rows,
+//                  for steps in which an expert gets 8 rows or more on average: moe_tcgen05.cu.)
 //                  Epilogues: relu(c)^2 * weight(row) in the compute type (the experts' first product), or
 //                  float (the second); moe_combine adds each token's rows up in the order of its choices.
 //   The float path has a plain FFMA kernel of the same shape.
@@ -236,117 +237,6 @@ __device__ __forceinline__ uint4 ld16_or_zero(const __nv_bfloat16* p, bool ok) {
 
 // MODE 0: C (compute type) = relu(c)^2 * row_w[row];  MODE 1: C (float) = c.
 // A [*, lda]: row src_row[r] (MODE 0) or r itself (src_row null).  W_e = W + e * w_expert_stride, rows at ldw.
-// DEPTH: steps of 32 k whose operands are loaded together (few rows: more bytes in flight per thread).
-template <int MT, int NT, int DEPTH, int MODE>
-__global__ void __launch_bounds__(128)
-moe_grouped_bf16_kernel(const __nv_bfloat16* __restrict__ A, int lda, const int* __restrict__ src_row,
-                        const __nv_bfloat16* __restrict__ W, int ldw, long long w_expert_stride,
-                        void* __restrict__ Cout, int ldc, const float* __restrict__ row_w,
-                        const int* __restrict__ tile_e, const int* __restrict__ tile_r0,
-                        const int* __restrict__ tile_n, int N, int K) {
-  ccb::pdl_begin();
-  const int tile = blockIdx.x;
-  const int n_rows = tile_n[tile];
-  if (n_rows <= 0) return;
-  const int e = tile_e[tile], r0 = tile_r0[tile];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int gid = lane >> 2, tig = lane & 3;
-  const int n_base = (blockIdx.y * 4 + warp) * (8 * NT);
-  if (n_base >= N) return;
-  const __nv_bfloat16* We = W + (size_t)e * w_expert_stride;
-
-  const __nv_bfloat16* arow[MT][2];
-#pragma unroll
-  for (int m = 0; m < MT; ++m)
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      int r = m * 16 + hh * 8 + gid;
-      if (r >= n_rows) r = n_rows - 1;   // a row of the tile anyway; its result is not stored
-      const int g = r0 + r;
-      arow[m][hh] = A + (size_t)(src_row ? src_row[g] : g) * lda;
-    }
-  const __nv_bfloat16* wrow[NT];
-  bool wok[NT];
-#pragma unroll
-  for (int n = 0; n < NT; ++n) {
-    const int col = n_base + n * 8 + gid;
-    wok[n] = col < N;
-    wrow[n] = We + (size_t)(wok[n] ? col : 0) * ldw;
-  }
-  float acc[MT][NT][4];
-#pragma unroll
-  for (int m = 0; m < MT; ++m)
-#pragma unroll
-    for (int n = 0; n < NT; ++n)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) acc[m][n][i] = 0.f;
-
-  uint4 a[DEPTH][MT][2], b[DEPTH][NT];
-  auto load = [&](int k0) {
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-      const int k = k0 + 32 * d + 8 * tig;
-      const bool ok = k < K;
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        a[d][m][0] = ld16_or_zero(arow[m][0] + k, ok);
-        a[d][m][1] = ld16_or_zero(arow[m][1] + k, ok);
-      }
-#pragma unroll
-      for (int n = 0; n < NT; ++n) b[d][n] = ld16_or_zero(wrow[n] + k, ok && wok[n]);
-    }
-  };
-  load(0);
-  for (int k0 = 0; k0 < K; k0 += 32 * DEPTH) {
-    uint4 ca[DEPTH][MT][2], cb[DEPTH][NT];
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d) {
-#pragma unroll
-      for (int m = 0; m < MT; ++m) ca[d][m][0] = a[d][m][0], ca[d][m][1] = a[d][m][1];
-#pragma unroll
-      for (int n = 0; n < NT; ++n) cb[d][n] = b[d][n];
-    }
-    if (k0 + 32 * DEPTH < K) load(k0 + 32 * DEPTH);   // the next operands are on their way during these products
-#pragma unroll
-    for (int d = 0; d < DEPTH; ++d)
-#pragma unroll
-      for (int m = 0; m < MT; ++m) {
-        const uint32_t f0[4] = {ca[d][m][0].x, ca[d][m][1].x, ca[d][m][0].y, ca[d][m][1].y};
-        const uint32_t f1[4] = {ca[d][m][0].z, ca[d][m][1].z, ca[d][m][0].w, ca[d][m][1].w};
-#pragma unroll
-        for (int n = 0; n < NT; ++n) {
-          mma_bf16_16816(acc[m][n], f0, cb[d][n].x, cb[d][n].y);
-          mma_bf16_16816(acc[m][n], f1, cb[d][n].z, cb[d][n].w);
-        }
-      }
-  }
-#pragma unroll
-  for (int m = 0; m < MT; ++m)
-#pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int r = m * 16 + hh * 8 + gid;
-      if (r >= n_rows) continue;
-      const size_t g = (size_t)(r0 + r);
-      const float wr = MODE == 0 ? row_w[g] : 1.f;
-#pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        const int col = n_base + n * 8 + 2 * tig;
-        float v0 = acc[m][n][hh * 2], v1 = acc[m][n][hh * 2 + 1];
-        if (MODE == 0) {
-          v0 = fmaxf(v0, 0.f); v1 = fmaxf(v1, 0.f);
-          v0 = v0 * v0 * wr; v1 = v1 * v1 * wr;
-          __nv_bfloat16* c = (__nv_bfloat16*)Cout + g * ldc + col;
-          if (col < N) c[0] = __float2bfloat16_rn(v0);
-          if (col + 1 < N) c[1] = __float2bfloat16_rn(v1);
-        } else {
-          float* c = (float*)Cout + g * ldc + col;
-          if (col < N) c[0] = v0;
-          if (col + 1 < N) c[1] = v1;
-        }
-      }
-    }
-}
-
 // Few rows an expert (tiles of 16, a decode step): the product is a stream of the chosen experts' matrices, and
 // what counts is bytes in flight.  A block takes 8 columns of a tile; its four warps take a quarter of k each
 // (four steps of 32 loaded at once, the next four on their way) and add their parts up through shared memory.
@@ -525,7 +415,7 @@ CCB_API int ccb_moe_sort(const int* idx, const float* wts, int pairs, int top, i
 }
 
 // mode 0: C (the compute type) [sorted rows, N] = relu(A[src_row] W_e^T)^2 * row_w;  mode 1: C (float) = A W_e^T
-// with A's rows the sorted rows themselves.  BM must be what moe_sort was given: 16, 32 or 64 (bfloat16), 16 (float).
+// with A's rows the sorted rows themselves.  Tiles of 16 rows (what moe_sort was given).
 CCB_API int ccb_moe_grouped(const void* A, int lda, const int* src_row, const void* W, int ldw,
                             long long w_expert_stride, void* C, int ldc, const float* row_w, const int* tile_e,
                             const int* tile_r0, const int* tile_n, int max_tiles, int N, int K, int BM, int mode,
@@ -547,27 +437,17 @@ CCB_API int ccb_moe_grouped(const void* A, int lda, const int* src_row, const vo
   if (K % 8 || lda % 8 || ldw % 8 || w_expert_stride % 8 || (reinterpret_cast<uintptr_t>(A) & 15) ||
       (reinterpret_cast<uintptr_t>(W) & 15))
     return CCB_REFUSE_SIZE;
-  // few rows an expert (tiles of 16): moe_grouped_rows16_kernel, 8 columns a block and k cut over its warps
-#define CCB_GROUPED(MT, NT, DEPTH, MODE)                                                                          \
-  ccb_launch(moe_grouped_bf16_kernel<MT, NT, DEPTH, MODE>, dim3(max_tiles, (N + 32 * NT - 1) / (32 * NT)), dim3(128), \
-             0, stream, (const __nv_bfloat16*)A, lda, src_row, (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, \
-             row_w, tile_e, tile_r0, tile_n, N, K)
-  if (BM == 16) {
-    dim3 grid16((N + 7) / 8, max_tiles);   // the tiles that hold rows come first in the list, and so do their blocks
-    if (mode == 0)
-      ccb_launch(moe_grouped_rows16_kernel<0>, grid16, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row,
-                 (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
-    else
-      ccb_launch(moe_grouped_rows16_kernel<1>, grid16, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row,
-                 (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
-  }
-  // many rows: 128 columns a block and one step of k in flight behind the one in use.  Measured and not kept
-  // (2,048 tokens, 32 experts of 1024 x 2048, 4 chosen): 64 columns a block with two steps in flight 0.79 against
-  // 0.63 ms for the whole part, 64 columns with one step 0.66 ms
-  else if (BM == 32) { if (mode == 0) CCB_GROUPED(2, 4, 1, 0); else CCB_GROUPED(2, 4, 1, 1); }
-  else if (BM == 64) { if (mode == 0) CCB_GROUPED(4, 4, 1, 0); else CCB_GROUPED(4, 4, 1, 1); }
-  else return CCB_REFUSE_SIZE;
-#undef CCB_GROUPED
+  // (tiles of more rows run on tcgen05: moe_tcgen05.cu.  An mma.sync form of this kernel for tiles of 32 and 64
+  // rows, 128 columns a block, was measured against it and taken out: about twice as slow, 313 against 143 us
+  // for the whole part at 128 tokens, 32 experts of 1536 x 4096 of which 4 are chosen)
+  if (BM != 16) return CCB_REFUSE_SIZE;
+  dim3 grid16((N + 7) / 8, max_tiles);   // the tiles that hold rows come first in the list, and so do their blocks
+  if (mode == 0)
+    ccb_launch(moe_grouped_rows16_kernel<0>, grid16, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row,
+               (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
+  else
+    ccb_launch(moe_grouped_rows16_kernel<1>, grid16, dim3(128), 0, stream, (const __nv_bfloat16*)A, lda, src_row,
+               (const __nv_bfloat16*)W, ldw, w_expert_stride, C, ldc, row_w, tile_e, tile_r0, tile_n, N, K);
   return ccb_launch_status();
 }
 

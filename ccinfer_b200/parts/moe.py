@@ -31,10 +31,13 @@ from .base import FeedForward, TensorSpec
 
 
 class MixtureOfExperts(FeedForward):
-    # from this many weights of the routed experts on, the sparse form runs (measured on B200: below, the dense
-    # form's two products cost less than the sparse form's extra launches)
-    SPARSE_MIN_WEIGHTS = 1 << 22
-    TC_MIN_ROWS_PER_EXPERT = 64   # (token, choice) pairs per expert from which the tcgen05 grouped product runs
+    # From this many weights of the routed experts on, the sparse form runs.  Measured on B200, bfloat16, 32 experts
+    # of which 4 are chosen, the whole part in us, dense / sparse at 1, 8, 256, 2,048 tokens: 16.8 M weights
+    # 22 / 26, 24 / 31, 37 / 51, 138 / 99; 67 M weights 47 / 33, 48 / 42, 75 / 78, 340 / 187.
+    SPARSE_MIN_WEIGHTS = 1 << 25
+    # (token, choice) pairs per expert from which the tcgen05 grouped product runs (402 M weights, 64 tokens, i.e.
+    # 8 pairs an expert: 131 us against 222 us for tiles of 16 rows on mma.sync)
+    TC_MIN_ROWS_PER_EXPERT = 8
 
     def __init__(self, hidden: int, experts: int, top: int, expert_ff: int, names: dict, groups: int = 1,
                  keep: int = 1, shared_ff: int = 0, activation: str = "relu2", sparse=None):
@@ -99,12 +102,10 @@ class MixtureOfExperts(FeedForward):
         i32, f32 = torch.int32, torch.float32
         idx, wts, _ = self.route(x, T)
         pairs, max_pairs = T * top, rt.max_tokens * top
-        # rows per tile: as many as an expert gets on average, so that its weights are read once per 16 to 64 rows;
-        # from 64 rows an expert on, tiles of 128 rows on tcgen05 (bfloat16)
+        # rows per tile: 16 (a decode step: the chosen experts' weights are streamed once per tile), or 128 on
+        # tcgen05 once an expert gets some rows on average (bfloat16)
         tc = rt.dtype == torch.bfloat16 and pairs >= self.TC_MIN_ROWS_PER_EXPERT * E
-        BM = 16 if (rt.dtype == f32 or pairs <= 16 * E) else (32 if pairs <= 32 * E else 64)
-        if tc:
-            BM = kernels.MOE_TC_ROWS
+        BM = kernels.MOE_TC_ROWS if tc else 16
         n_tiles = kernels.moe_max_tiles(pairs, E, BM)
         cap = kernels.moe_max_tiles(max_pairs, E, 16)
         src_row = rt.scratch.get("moe_src_row", (max_pairs,), i32)
