@@ -108,15 +108,17 @@ class MixtureOfExperts(FeedForward):
         BM = kernels.MOE_TC_ROWS if tc else 16
         n_tiles = kernels.moe_max_tiles(pairs, E, BM)
         cap = kernels.moe_max_tiles(max_pairs, E, 16)
-        src_row = rt.scratch.get("moe_src_row", (max_pairs,), i32)
-        row_w = rt.scratch.get("moe_row_w", (max_pairs,), f32)
-        pair_pos = rt.scratch.get("moe_pair_pos", (max_pairs,), i32)
-        tiles = [rt.scratch.get(f"moe_tile{k}", (cap,), i32)[:n_tiles] for k in range(3)]
+        # (layers of other sizes have buffers of their own: a buffer that only long steps use must not grow once
+        # CUDA graphs hold the pool's addresses)
+        src_row = rt.scratch.get(f"moe_src_row:{top}", (max_pairs,), i32)
+        row_w = rt.scratch.get(f"moe_row_w:{top}", (max_pairs,), f32)
+        pair_pos = rt.scratch.get(f"moe_pair_pos:{top}", (max_pairs,), i32)
+        tiles = [rt.scratch.get(f"moe_tile{k}:{top}:{E}", (cap,), i32)[:n_tiles] for k in range(3)]
         kernels.moe_sort(idx, wts, E, BM, src_row, row_w, pair_pos, *tiles)
-        act = rt.scratch.get("moe_act_rows", (max_pairs, F), rt.dtype)[:pairs]
-        rows = rt.scratch.get("moe_out_rows", (max_pairs, D), f32)[:pairs]
+        act = rt.scratch.get(f"moe_act_rows:{top}:{F}", (max_pairs, F), rt.dtype)[:pairs]
+        rows = rt.scratch.get(f"moe_out_rows:{top}", (max_pairs, D), f32)[:pairs]
         if tc:
-            xs = rt.scratch.get("moe_x_sorted", (max_pairs, D), rt.dtype)[:pairs]
+            xs = rt.scratch.get(f"moe_x_sorted:{top}", (max_pairs, D), rt.dtype)[:pairs]
             kernels.moe_gather_rows(xs, x, src_row)
             kernels.moe_grouped_tc(act, xs, self.w_up, row_w, *tiles, F, D, F, 0, status=rt.status)
             kernels.moe_grouped_tc(rows, act, self.w_down, row_w, *tiles, D, F, F, 1, status=rt.status)
@@ -125,7 +127,7 @@ class MixtureOfExperts(FeedForward):
             kernels.moe_grouped(rows, act, None, self.w_down, F, row_w, *tiles, D, F, BM, 1)
         shared = None
         if self.SF:
-            sa = rt.scratch.get("moe_shared_act", (rt.max_tokens, self.SF), rt.dtype)[:T]
+            sa = rt.scratch.get(f"moe_shared_act:{self.SF}", (rt.max_tokens, self.SF), rt.dtype)[:T]
             rt.linear(sa, x, self.w_shared_up)
             kernels.moe_dense_act(sa, wts, 0, 1, self.SF)
             shared = rt.scratch.get("moe_shared_out", (rt.max_tokens, D), rt.dtype)[:T]
