@@ -654,3 +654,19 @@ def test_the_programs_as_a_user_calls_them(models, tmp_path):
             seen[e["id"]] += len(e["tokens"])
     assert len(rows) == sum(len(x) for x in reqs.values())
     helpers.compare(rows, ref, TOL32, "trace_run")
+
+
+@gpu
+def test_a_preempted_request_starts_its_state_again(models):
+    """So few pages that a request is preempted and computed again (its slot is closed and opened: the recurrent
+    state starts from zero, the windows' pages are taken anew): the greedy tokens are those of a calm run."""
+    from ccinfer_b200 import LLM, SamplingParams
+    d, cfg, w, reqs, ref, page = models["A", "float32"]
+    rng = np.random.RandomState(6)
+    prompts = [rng.randint(0, cfg["vocab"], size=n).tolist() for n in (20, 26, 17)]
+    llm = LLM(d, dtype="float32", page_size=page, kv_tokens=8 * page, prefill_chunk_size=16, max_requests=4,
+              max_tokens_per_step=64)
+    got = llm.generate(prompts, [SamplingParams(max_tokens=n) for n in (24, 20, 28)])
+    assert llm.scheduler.preemptions > 0
+    assert got == [plain.greedy(cfg, w, p, n) for p, n in zip(prompts, (24, 20, 28))]
+    llm.engine.cache.check_consistency()
