@@ -233,10 +233,44 @@ __global__ void concat_cast_kernel(T* __restrict__ out, const float* __restrict_
   }
 }
 
+// four columns a thread (D a multiple of 4, 16-byte bases)
+template <typename T>
+__global__ void concat_cast_vec_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b,
+                                       int D, size_t total4) {
+  ccb::pdl_begin();
+  const int d4 = D >> 1;   // groups of four in a row of 2 D
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / d4;
+    const int c = (int)(i - t * d4) * 4;
+    const float4 v = *reinterpret_cast<const float4*>(c < D ? a + t * D + c : b + t * D + c - D);
+    T* dst = out + t * 2 * (size_t)D + c;
+    if constexpr (sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(dst) = v;
+    } else {
+      const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+      uint2 r;
+      r.x = *reinterpret_cast<const uint32_t*>(&lo);
+      r.y = *reinterpret_cast<const uint32_t*>(&hi);
+      *reinterpret_cast<uint2*>(dst) = r;
+    }
+  }
+}
+
 CCB_API int ccb_concat_cast(void* out, const float* a, const float* b, int rows, int D, int dtype,
                             cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (D <= 0) return CCB_REFUSE_SIZE;
+  if (D % 4 == 0 && (dtype == CCB_F32 || dtype == CCB_BF16) &&
+      ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0) {
+    const size_t total4 = (size_t)rows * (D / 2);
+    const int blocks4 = (int)((total4 + 255) / 256 < 65535 * 8 ? (total4 + 255) / 256 : 65535 * 8);
+    if (dtype == CCB_F32)
+      ccb_launch(concat_cast_vec_kernel<float>, dim3(blocks4), dim3(256), 0, stream, (float*)out, a, b, D, total4);
+    else
+      ccb_launch(concat_cast_vec_kernel<__nv_bfloat16>, dim3(blocks4), dim3(256), 0, stream, (__nv_bfloat16*)out, a, b,
+                 D, total4);
+    return ccb_launch_status();
+  }
   const size_t total = (size_t)rows * 2 * D;
   const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
   if (dtype == CCB_F32)

@@ -119,6 +119,50 @@ moe_dense_act_kernel(T* __restrict__ act, int ld, const float* __restrict__ dens
   }
 }
 
+// Four columns a thread (all widths, the row stride and the base multiples of four columns): the four lie in one
+// expert's columns.
+template <typename T> struct Row4;
+template <> struct Row4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Row4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&r.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 r;
+    r.x = *reinterpret_cast<const uint32_t*>(&a);
+    r.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_dense_act_vec_kernel(T* __restrict__ act, int ld, const float* __restrict__ dense_w, int rows, int E, int F,
+                         int shared) {
+  ccb::pdl_begin();
+  const int w4 = (E * F + shared) >> 2;
+  const size_t total = (size_t)rows * w4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / w4;
+    const int c = (int)(i - t * w4) * 4;
+    T* p = act + t * ld + c;
+    float4 u = Row4<T>::load(p);
+    u.x = fmaxf(u.x, 0.f); u.y = fmaxf(u.y, 0.f); u.z = fmaxf(u.z, 0.f); u.w = fmaxf(u.w, 0.f);
+    float w = 1.f;
+    if (c < E * F) w = dense_w[t * E + c / F];
+    if (w == 0.f) u = make_float4(0.f, 0.f, 0.f, 0.f);   // an expert that was not chosen gives exact zeros
+    else u = make_float4(u.x * u.x * w, u.y * u.y * w, u.z * u.z * w, u.w * u.w * w);
+    Row4<T>::store(p, u);
+  }
+}
+
 }  // namespace
 
 CCB_API int ccb_moe_route(const float* logits, int ldl, const float* correction, int* idx, float* wts,
@@ -139,6 +183,18 @@ CCB_API int ccb_moe_dense_act(void* act, int ld, const float* dense_w, int rows,
                               cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (E < 0 || F <= 0 || shared < 0 || ld < E * F + shared) return CCB_REFUSE_SIZE;
+  if (dtype != CCB_F32 && dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
+  if ((E == 0 || F % 4 == 0) && shared % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(act) & 15) == 0) {
+    const size_t total4 = (size_t)rows * ((E * F + shared) / 4);
+    const int blocks4 = (int)((total4 + 255) / 256 < 65535 * 8 ? (total4 + 255) / 256 : 65535 * 8);
+    if (dtype == CCB_F32)
+      ccb_launch(moe_dense_act_vec_kernel<float>, dim3(blocks4), dim3(256), 0, stream, (float*)act, ld, dense_w, rows,
+                 E, F, shared);
+    else
+      ccb_launch(moe_dense_act_vec_kernel<__nv_bfloat16>, dim3(blocks4), dim3(256), 0, stream, (__nv_bfloat16*)act, ld,
+                 dense_w, rows, E, F, shared);
+    return ccb_launch_status();
+  }
   const size_t total = (size_t)rows * (E * F + shared);
   const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
   if (dtype == CCB_F32)
@@ -398,6 +454,32 @@ moe_combine_kernel(T* __restrict__ out, const float* __restrict__ rows, const in
   }
 }
 
+// the same, four columns a thread (D a multiple of 4, 16-byte rows)
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_vec_kernel(T* __restrict__ out, const float* __restrict__ rows, const int* __restrict__ pair_pos,
+                       const T* __restrict__ shared, int top, int D, size_t total4) {
+  ccb::pdl_begin();
+  const int d4 = D >> 2;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = i / d4;
+    const int c = (int)(i - t * d4) * 4;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int k = 0; k < top; ++k) {
+      const int pos = pair_pos[t * top + k];
+      if (pos >= 0) {
+        const float4 x = *reinterpret_cast<const float4*>(rows + (size_t)pos * D + c);
+        v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+      }
+    }
+    if (shared) {
+      const float4 x = Row4<T>::load(shared + t * D + c);
+      v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+    }
+    Row4<T>::store(out + t * D + c, v);
+  }
+}
+
 }  // namespace
 
 CCB_API int ccb_moe_sort(const int* idx, const float* wts, int pairs, int top, int E, int BM, int max_tiles,
@@ -455,6 +537,19 @@ CCB_API int ccb_moe_combine(void* out, const float* rows, const int* pair_pos, c
                             int D, int dtype, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (top <= 0 || D <= 0) return CCB_REFUSE_SIZE;
+  if (dtype != CCB_F32 && dtype != CCB_BF16) return CCB_REFUSE_DTYPE;
+  if (D % 4 == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(rows) |
+                      reinterpret_cast<uintptr_t>(shared)) & 15) == 0) {
+    const size_t total4 = (size_t)tokens * (D / 4);
+    const int blocks4 = (int)((total4 + 255) / 256 < 65535 * 8 ? (total4 + 255) / 256 : 65535 * 8);
+    if (dtype == CCB_F32)
+      ccb_launch(moe_combine_vec_kernel<float>, dim3(blocks4), dim3(256), 0, stream, (float*)out, rows, pair_pos,
+                 (const float*)shared, top, D, total4);
+    else
+      ccb_launch(moe_combine_vec_kernel<__nv_bfloat16>, dim3(blocks4), dim3(256), 0, stream, (__nv_bfloat16*)out, rows,
+                 pair_pos, (const __nv_bfloat16*)shared, top, D, total4);
+    return ccb_launch_status();
+  }
   const size_t total = (size_t)tokens * D;
   const int blocks = (int)((total + 255) / 256 < 65535 * 8 ? (total + 255) / 256 : 65535 * 8);
   if (dtype == CCB_F32)
