@@ -44,8 +44,11 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int oc, const 
   const int half = rot_dims >> 1;
   const int slot = slot_map ? slot_map[t] : -1;
   const bool keep = slot >= 0;
-  if (keep && slot >= num_slots) set_status(status, CCB_ST_BAD_SLOT);
-  if (keep && slot < num_slots) {
+  // the token's blocks share the work: block 0 of the row makes the cache row, the others the queries' rotated
+  // parts (all of it in one block when the grid has one block a token)
+  const int parts = gridDim.y;
+  if (blockIdx.y == 0 && keep && slot >= num_slots) set_status(status, CCB_ST_BAD_SLOT);
+  if (blockIdx.y == 0 && keep && slot < num_slots) {
     float ss = 0.f;
     for (int i = threadIdx.x; i < R; i += kPrepThreads) {
       const float v = to_f32(row[oc + i]);
@@ -70,7 +73,11 @@ latent_prepare_kernel(const T* __restrict__ proj, int ld, int oq, int oc, const 
       dst[R + i] = from_f32<T>(v);
     }
   }
-  for (int i = threadIdx.x; i < H * r; i += kPrepThreads) {
+  const int q_total = H * r;
+  const int q_per = parts > 1 ? (q_total + parts - 2) / (parts - 1) : q_total;
+  const int q_lo = (parts > 1 && blockIdx.y > 0) ? ((int)blockIdx.y - 1) * q_per : 0;
+  const int q_hi = parts > 1 ? (blockIdx.y == 0 ? 0 : min(q_total, q_lo + q_per)) : q_total;
+  for (int i = q_lo + threadIdx.x; i < q_hi; i += kPrepThreads) {
     const int h = i / r, k = i - h * r;
     const T* qr = row + oq + (size_t)h * (d + r) + d;
     float v;
@@ -556,11 +563,15 @@ CCB_API int ccb_latent_prepare(const void* proj, int ld, int oq, int oc, const f
   if (T <= 0) return 0;
   if (H <= 0 || d < 0 || r < 0 || R <= 0 || rot_dims < 0 || rot_dims > r || (rot_dims & 1)) return CCB_REFUSE_SIZE;
   if (rot_dims > 0 && inv_freq == nullptr) return CCB_REFUSE_ARG;
+  // few tokens: a token's work is spread over several blocks (the cache row, and the heads' rotated parts in
+  // pieces of about 512 coordinates)
+  const int parts = T <= 64 ? 1 + min(8, (H * r + 511) / 512) : 1;
+  const dim3 grid(T, parts);
   if (dtype == CCB_F32)
-    ccb_launch(latent_prepare_kernel<float>, dim3(T), dim3(kPrepThreads), 0, stream, (const float*)proj, ld, oq, oc, w,
+    ccb_launch(latent_prepare_kernel<float>, grid, dim3(kPrepThreads), 0, stream, (const float*)proj, ld, oq, oc, w,
                inv_freq, rot_dims, positions, slot_map, (float*)cache, num_slots, qa, H, d, r, R, eps, status);
   else if (dtype == CCB_BF16)
-    ccb_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(kPrepThreads), 0, stream,
+    ccb_launch(latent_prepare_kernel<__nv_bfloat16>, grid, dim3(kPrepThreads), 0, stream,
                (const __nv_bfloat16*)proj, ld, oq, oc, w, inv_freq, rot_dims, positions, slot_map,
                (__nv_bfloat16*)cache, num_slots, qa, H, d, r, R, eps, status);
   else

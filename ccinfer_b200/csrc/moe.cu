@@ -28,17 +28,11 @@ __device__ __forceinline__ void warp_argmax(float& v, int& i) {
   }
 }
 
-// shared memory per warp: s[E], c[E], gs[groups]
-__global__ void __launch_bounds__(kRouteWarps * 32)
-moe_route_kernel(const float* __restrict__ logits, int ldl, const float* __restrict__ correction,
-                 int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ dense_w, int rows, int E,
-                 int groups, int keep, int top) {
-  ccb::pdl_begin();
-  extern __shared__ float smem[];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * kRouteWarps + warp;
-  if (t >= rows) return;
-  float* s = smem + (size_t)warp * (2 * E + groups);
+// One token's choice by one warp; s: 2 E + groups floats of shared memory of the warp's own (s[E], c[E], gs[groups]).
+__device__ __forceinline__ void route_token(const float* __restrict__ logits, int ldl,
+                                            const float* __restrict__ correction, int* __restrict__ idx,
+                                            float* __restrict__ wts, float* __restrict__ dense_w, int t, int E,
+                                            int groups, int keep, int top, float* s, int lane) {
   float* c = s + E;
   float* gs = c + E;
   const float* z = logits + (size_t)t * ldl;
@@ -96,6 +90,20 @@ moe_route_kernel(const float* __restrict__ logits, int ldl, const float* __restr
     }
     __syncwarp();
   }
+}
+
+// shared memory: a warp's scratch of route_token per warp
+__global__ void __launch_bounds__(kRouteWarps * 32)
+moe_route_kernel(const float* __restrict__ logits, int ldl, const float* __restrict__ correction,
+                 int* __restrict__ idx, float* __restrict__ wts, float* __restrict__ dense_w, int rows, int E,
+                 int groups, int keep, int top) {
+  ccb::pdl_begin();
+  extern __shared__ float smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x * kRouteWarps + warp;
+  if (t >= rows) return;
+  route_token(logits, ldl, correction, idx, wts, dense_w, t, E, groups, keep, top,
+              smem + (size_t)warp * (2 * E + groups), lane);
 }
 
 template <typename T>
@@ -231,19 +239,20 @@ constexpr int kSortThreads = 1024;
 
 // idx, wts [pairs] (pairs = tokens * top).  Outputs: src_row [pairs] (token of a sorted row), row_w [pairs],
 // pair_pos [pairs] (sorted row of a pair), tile_e / tile_r0 / tile_n [max_tiles].
-__global__ void __launch_bounds__(kSortThreads)
-moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int pairs, int top, int E, int BM,
-                int max_tiles, int* __restrict__ src_row, float* __restrict__ row_w, int* __restrict__ pair_pos,
-                int* __restrict__ tile_e, int* __restrict__ tile_r0, int* __restrict__ tile_n) {
-  ccb::pdl_begin();
-  extern __shared__ int sm[];
+// The whole block; sm: 4 E + 2 ints of shared memory.
+__device__ __forceinline__ void sort_pairs(const int* __restrict__ idx, const float* __restrict__ wts, int pairs,
+                                           int top, int E, int BM, int max_tiles, int* __restrict__ src_row,
+                                           float* __restrict__ row_w, int* __restrict__ pair_pos,
+                                           int* __restrict__ tile_e, int* __restrict__ tile_r0,
+                                           int* __restrict__ tile_n, int* sm) {
+  const int kSortStride = blockDim.x;
   int* counts = sm;             // [E]
   int* offs = sm + E;           // [E + 1]
   int* tstart = offs + E + 1;   // [E + 1]
   int* cursor = tstart + E + 1; // [E]
-  for (int e = threadIdx.x; e < E; e += kSortThreads) counts[e] = 0, cursor[e] = 0;
+  for (int e = threadIdx.x; e < E; e += kSortStride) counts[e] = 0, cursor[e] = 0;
   __syncthreads();
-  for (int p = threadIdx.x; p < pairs; p += kSortThreads) {
+  for (int p = threadIdx.x; p < pairs; p += kSortStride) {
     const int e = idx[p];
     if (e >= 0 && e < E) atomicAdd(&counts[e], 1);
   }
@@ -260,7 +269,7 @@ moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int 
     tstart[E] = t;
   }
   __syncthreads();
-  for (int p = threadIdx.x; p < pairs; p += kSortThreads) {
+  for (int p = threadIdx.x; p < pairs; p += kSortStride) {
     const int e = idx[p];
     if (e < 0 || e >= E) { pair_pos[p] = -1; continue; }
     const int pos = offs[e] + atomicAdd(&cursor[e], 1);
@@ -268,7 +277,7 @@ moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int 
     row_w[pos] = wts[p];
     pair_pos[p] = pos;
   }
-  for (int t = threadIdx.x; t < max_tiles; t += kSortThreads) {
+  for (int t = threadIdx.x; t < max_tiles; t += kSortStride) {
     int n = 0, e = 0, r0 = 0;
     if (t < tstart[E]) {
       int lo = 0, hi = E - 1;   // the last expert whose first tile is <= t and that has tiles
@@ -285,6 +294,35 @@ moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int 
     tile_r0[t] = r0;
     tile_n[t] = n;
   }
+}
+
+__global__ void __launch_bounds__(kSortThreads)
+moe_sort_kernel(const int* __restrict__ idx, const float* __restrict__ wts, int pairs, int top, int E, int BM,
+                int max_tiles, int* __restrict__ src_row, float* __restrict__ row_w, int* __restrict__ pair_pos,
+                int* __restrict__ tile_e, int* __restrict__ tile_r0, int* __restrict__ tile_n) {
+  ccb::pdl_begin();
+  extern __shared__ int sm[];
+  sort_pairs(idx, wts, pairs, top, E, BM, max_tiles, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n, sm);
+}
+
+// Steps of few tokens: the router and the sort in one block, a warp a token (up to 32 tokens).
+// Shared memory: the sort's 4 E + 2 ints, then a warp's scratch of route_token per token.
+__global__ void __launch_bounds__(kSortThreads)
+moe_route_sort_kernel(const float* __restrict__ logits, int ldl, const float* __restrict__ correction,
+                      int* __restrict__ idx, float* __restrict__ wts, int rows, int E, int groups, int keep, int top,
+                      int BM, int max_tiles, int* __restrict__ src_row, float* __restrict__ row_w,
+                      int* __restrict__ pair_pos, int* __restrict__ tile_e, int* __restrict__ tile_r0,
+                      int* __restrict__ tile_n) {
+  ccb::pdl_begin();
+  extern __shared__ int sm[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* scratch = reinterpret_cast<float*>(sm + 4 * E + 2);
+  if (warp < rows)
+    route_token(logits, ldl, correction, idx, wts, nullptr, warp, E, groups, keep, top,
+                scratch + (size_t)warp * (2 * E + groups), lane);
+  __threadfence_block();
+  __syncthreads();   // the choices are written: the same block sorts them
+  sort_pairs(idx, wts, rows * top, top, E, BM, max_tiles, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n, sm);
 }
 
 __device__ __forceinline__ uint4 ld16_or_zero(const __nv_bfloat16* p, bool ok) {
@@ -493,6 +531,22 @@ CCB_API int ccb_moe_sort(const int* idx, const float* wts, int pairs, int top, i
   cudaFuncSetAttribute(moe_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   ccb_launch(moe_sort_kernel, dim3(1), dim3(kSortThreads), smem, stream, idx, wts, pairs, top, E, BM, max_tiles,
              src_row, row_w, pair_pos, tile_e, tile_r0, tile_n);
+  return ccb_launch_status();
+}
+
+// ccb_moe_route and ccb_moe_sort in one kernel, for up to 32 tokens (no dense row of weights).
+CCB_API int ccb_moe_route_sort(const float* logits, int ldl, const float* correction, int* idx, float* wts, int rows,
+                               int E, int groups, int keep, int top, int BM, int max_tiles, int* src_row, float* row_w,
+                               int* pair_pos, int* tile_e, int* tile_r0, int* tile_n, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (rows > 32 || E <= 0 || top <= 0 || top > E || groups <= 0 || E % groups || keep <= 0 || keep > groups ||
+      top > (E / groups) * keep || BM <= 0 || max_tiles < min(rows * top, (rows * top + BM - 1) / BM + E))
+    return CCB_REFUSE_SIZE;
+  const size_t smem = (size_t)(4 * E + 2) * sizeof(int) + (size_t)rows * (2 * E + groups) * sizeof(float);
+  if (smem > 96 * 1024) return CCB_REFUSE_SIZE;
+  cudaFuncSetAttribute(moe_route_sort_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  ccb_launch(moe_route_sort_kernel, dim3(1), dim3(kSortThreads), smem, stream, logits, ldl, correction, idx, wts, rows,
+             E, groups, keep, top, BM, max_tiles, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n);
   return ccb_launch_status();
 }
 

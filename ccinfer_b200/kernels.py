@@ -94,6 +94,8 @@ _SIGNATURES = {
     "ccb_moe_dense_act": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_moe_sort": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                      c_void_p, c_void_p, c_void_p],
+    "ccb_moe_route_sort": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "ccb_moe_grouped": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_void_p, c_void_p,
                         c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "ccb_moe_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
@@ -616,6 +618,26 @@ def moe_sort(idx, wts, E: int, BM: int, src_row, row_w, pair_pos, tile_e, tile_r
     assert tile_r0.numel() >= n_tiles and tile_n.numel() >= n_tiles and n_tiles >= moe_max_tiles(T * top, E, BM)
     _check(lib().ccb_moe_sort(_p(idx), _p(wts), T * top, top, E, BM, n_tiles, _p(src_row), _p(row_w), _p(pair_pos),
                               _p(tile_e), _p(tile_r0), _p(tile_n), _stream()), "moe_sort")
+
+
+MOE_ROUTE_SORT_MAX_TOKENS = 32
+
+
+def moe_route_sort(logits, correction, idx, wts, groups: int, keep: int, E: int, BM: int, src_row, row_w, pair_pos,
+                   tile_e, tile_r0, tile_n) -> None:
+    """``moe_route`` (without the dense row) and ``moe_sort`` as one kernel, for steps of up to
+    MOE_ROUTE_SORT_MAX_TOKENS tokens."""
+    _cuda(correction, idx, wts, src_row, row_w, pair_pos, tile_e, tile_r0, tile_n)
+    T, top = idx.shape
+    n_tiles = tile_e.numel()
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape == (T, E)
+    assert idx.dtype == torch.int32 and idx.is_contiguous() and wts.dtype == torch.float32 and wts.shape == (T, top)
+    assert correction is None or (correction.dtype == torch.float32 and correction.numel() == E)
+    assert src_row.numel() >= T * top and row_w.numel() >= T * top and pair_pos.numel() >= T * top
+    assert tile_r0.numel() >= n_tiles and tile_n.numel() >= n_tiles and n_tiles >= moe_max_tiles(T * top, E, BM)
+    _check(lib().ccb_moe_route_sort(_p(logits), logits.stride(0), _p(correction), _p(idx), _p(wts), T, E, int(groups),
+                                    int(keep), top, BM, n_tiles, _p(src_row), _p(row_w), _p(pair_pos), _p(tile_e),
+                                    _p(tile_r0), _p(tile_n), _stream()), "moe_route_sort")
 
 
 def moe_grouped(c, a, src_row, w, w_expert_stride: int, row_w, tile_e, tile_r0, tile_n, N: int, K: int, BM: int,

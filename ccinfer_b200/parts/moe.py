@@ -85,22 +85,28 @@ class MixtureOfExperts(FeedForward):
         self.w_up = torch.cat(ups, dim=0).contiguous()        # [E F (+ SF), D]
         self.w_down = torch.cat(downs, dim=1).contiguous()    # [D, E F (+ SF)]
 
-    def route(self, x, T):
-        """idx int32 [T, top], wts float [T, top], dense float [T, E] for the rows of x."""
+    def route(self, x, T, sort_into=None):
+        """idx int32 [T, top], wts float [T, top], dense float [T, E] for the rows of x.  ``sort_into`` (BM and the
+        arrays of ``kernels.moe_sort``): the pairs are sorted by expert as well, in the same kernel where the step
+        has few tokens (then there is no dense row)."""
         rt = self.rt
         logits = rt.scratch.get("moe_logits", (rt.max_tokens, self.E), torch.float32)[:T]
         rt.linear(logits, x, self.w_router)
         idx = rt.scratch.get("moe_idx", (rt.max_tokens, self.top), torch.int32)[:T]
         wts = rt.scratch.get("moe_wts", (rt.max_tokens, self.top), torch.float32)[:T]
+        if sort_into is not None and T <= kernels.MOE_ROUTE_SORT_MAX_TOKENS:
+            kernels.moe_route_sort(logits, self.correction, idx, wts, self.groups, self.keep, self.E, *sort_into)
+            return idx, wts, None
         dense = rt.scratch.get("moe_dense", (rt.max_tokens, self.E), torch.float32)[:T]
         kernels.moe_route(logits, self.correction, idx, wts, dense, self.groups, self.keep)
+        if sort_into is not None:
+            kernels.moe_sort(idx, wts, self.E, *sort_into)
         return idx, wts, dense
 
     def _forward_sparse(self, x, T):
         rt = self.rt
         E, F, D, top = self.E, self.F, self.hidden, self.top
         i32, f32 = torch.int32, torch.float32
-        idx, wts, _ = self.route(x, T)
         pairs, max_pairs = T * top, rt.max_tokens * top
         # rows per tile: 16 (a decode step: the chosen experts' weights are streamed once per tile), or 128 on
         # tcgen05 once an expert gets some rows on average (bfloat16)
@@ -114,7 +120,7 @@ class MixtureOfExperts(FeedForward):
         row_w = rt.scratch.get(f"moe_row_w:{top}", (max_pairs,), f32)
         pair_pos = rt.scratch.get(f"moe_pair_pos:{top}", (max_pairs,), i32)
         tiles = [rt.scratch.get(f"moe_tile{k}:{top}:{E}", (cap,), i32)[:n_tiles] for k in range(3)]
-        kernels.moe_sort(idx, wts, E, BM, src_row, row_w, pair_pos, *tiles)
+        idx, wts, _ = self.route(x, T, sort_into=(BM, src_row, row_w, pair_pos, *tiles))
         act = rt.scratch.get(f"moe_act_rows:{top}:{F}", (max_pairs, F), rt.dtype)[:pairs]
         rows = rt.scratch.get(f"moe_out_rows:{top}", (max_pairs, D), f32)[:pairs]
         if tc:
