@@ -222,6 +222,7 @@ CCB_API int ccb_moe_dense_act(void* act, int ld, const float* dense_w, int rows,
 //
 //   moe_sort       one block: counts per expert, their prefix sums, the place of every pair among its expert's
 //                  rows (pair_pos), the token and weight of every sorted row, and the list of tiles
+//   moe_route_sort the router and the sort as ONE block for steps of up to 32 tokens (a warp a token)
 //   moe_grouped    C[row, :] = A[src(row), :] W_e^T for the rows of every tile of 16, W_e the tile's expert:
 //                  bfloat16 on mma.sync m16n8k16 with float sums.  Both operands go from global memory straight
 //                  into the fragments: a thread loads 8 neighbouring k of its rows with ONE 16-byte access and
